@@ -70,7 +70,7 @@ class KVView:
     """One run's keys and values, with the page lists of the step's sequences."""
 
     k_pages: torch.Tensor  # [pages, kv heads, PAGE_SIZE, head size]
-    v_pages: torch.Tensor
+    v_pages: Optional[torch.Tensor]  # None for a group without values
     block_table: Optional[torch.Tensor]  # int32 [S, width] on the device, set per step
     window: int
 
@@ -92,7 +92,8 @@ class KVGroup:
         # zero-filled once: a page that was never written holds finite values, which the
         # attention kernels rely on when they multiply masked scores by unread rows
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        # a need without values (one latent row per position, from which the mixer makes keys and values) has no value pages
+        self.v = torch.zeros(shape, dtype=dtype, device=device) if need.values else None
         self.pages: Dict[int, List[int]] = {}  # slot -> page id per page index (-1: given back)
         self.first_held: Dict[int, int] = {}  # slot -> lowest page index still held
         # the same page lists as one matrix [slot, page index] (0 where nothing is held), kept in
@@ -107,7 +108,7 @@ class KVGroup:
         self.table[slot, index] = max(page, 0)
 
     def bytes(self) -> int:
-        return 2 * self.k.numel() * self.k.element_size()
+        return (2 if self.v is not None else 1) * self.k.numel() * self.k.element_size()
 
     def first_needed_page(self, next_pos: int) -> int:
         """Lowest page index that a query at `next_pos` or later can still read."""
@@ -157,7 +158,7 @@ class Cache:
             for need, runs in by_need.items():
                 if isinstance(need, KVNeed):
                     size = torch.empty((), dtype=need.dtype or dtype).element_size()
-                    asked += 2 * len(runs) * self.n_pages * need.num_kv_heads * PAGE_SIZE * need.head_dim * size
+                    asked += (2 if need.values else 1) * len(runs) * self.n_pages * need.num_kv_heads * PAGE_SIZE * need.head_dim * size
                 else:
                     n = torch.empty((), dtype=need.dtype).element_size() * max_seqs * len(runs)
                     for s in need.shape:
@@ -342,7 +343,7 @@ class Cache:
         family, gi, j = self.where(run)
         if family == "kv":
             g = self.kv_groups[gi]
-            return KVView(g.k[j], g.v[j], None if tables is None else tables[gi], g.need.window)
+            return KVView(g.k[j], None if g.v is None else g.v[j], None if tables is None else tables[gi], g.need.window)
         return StateView(self.state_groups[gi].state[j])
 
     def check_consistent(self) -> None:

@@ -167,6 +167,10 @@ class LlamaConfig:
             if not 0 <= t < self.vocab_size:
                 raise ConfigError(f"special token id {t} is outside the vocabulary of {self.vocab_size}")
         self.rope_scaling.validate()
+        if self.rope_scaling.kind == "yarn":
+            # its cosines and sines carry a magnitude factor, which the fused rotation and cache write of
+            # grouped-query attention does not apply
+            raise ConfigError("unsupported rope_scaling type 'yarn' for this architecture (known: default, linear, llama3)")
 
     def to_json(self) -> dict:
         d = {

@@ -22,8 +22,12 @@ from ..errors import ConfigError
 class RopeScaling:
     """The `rope_scaling` block of config.json.
 
-    kind: "none", "linear" or "llama3" (src/config.rs:13-40; the reference also
-    has YaRN, which no Llama checkpoint uses and which is not accepted here).
+    kind: "none", "linear", "llama3" (src/config.rs:13-40) or "yarn".
+
+    "yarn": pairs that turn more than `beta_fast` times over the original context keep their
+    frequency, pairs that turn less than `beta_slow` times are slowed by `factor`, a linear ramp
+    over the pair index lies between; cosines and sines are multiplied by 0.1 ln(factor) + 1
+    (`magnitude`).
     """
 
     kind: str = "none"
@@ -31,6 +35,8 @@ class RopeScaling:
     low_freq_factor: float = 1.0
     high_freq_factor: float = 4.0
     original_max_position_embeddings: int = 0
+    beta_fast: float = 32.0
+    beta_slow: float = 1.0
 
     @classmethod
     def from_json(cls, block: Optional[Mapping[str, Any]]) -> "RopeScaling":
@@ -59,14 +65,33 @@ class RopeScaling:
                 high_freq_factor=float(block.get("high_freq_factor", 4.0)),
                 original_max_position_embeddings=int(block["original_max_position_embeddings"]),
             )
+        if kind == "yarn":
+            for key in ("factor", "original_max_position_embeddings"):
+                if key not in block:
+                    raise ConfigError(f"rope_scaling of type 'yarn' needs '{key}'")
+            return cls(
+                kind="yarn",
+                factor=float(block["factor"]),
+                original_max_position_embeddings=int(block["original_max_position_embeddings"]),
+                beta_fast=float(block.get("beta_fast", 32.0)),
+                beta_slow=float(block.get("beta_slow", 1.0)),
+            )
         # The reference rejects an unknown type instead of guessing (src/model.rs:541-545).
-        raise ConfigError(f"unsupported rope_scaling type '{kind}' (known: default, linear, llama3)")
+        raise ConfigError(f"unsupported rope_scaling type '{kind}' (known: default, linear, llama3, yarn)")
 
     def to_json(self) -> Optional[dict]:
         if self.kind == "none":
             return None
         if self.kind == "linear":
             return {"rope_type": "linear", "factor": self.factor}
+        if self.kind == "yarn":
+            return {
+                "rope_type": "yarn",
+                "factor": self.factor,
+                "original_max_position_embeddings": self.original_max_position_embeddings,
+                "beta_fast": self.beta_fast,
+                "beta_slow": self.beta_slow,
+            }
         return {
             "rope_type": "llama3",
             "factor": self.factor,
@@ -76,10 +101,15 @@ class RopeScaling:
         }
 
     def validate(self) -> None:
-        if self.kind not in ("none", "linear", "llama3"):
+        if self.kind not in ("none", "linear", "llama3", "yarn"):
             raise ConfigError(f"unsupported rope scaling kind '{self.kind}'")
         if self.kind != "none" and not (math.isfinite(self.factor) and self.factor > 0):
             raise ConfigError(f"rope_scaling.factor must be finite and positive, got {self.factor}")
+        if self.kind == "yarn":
+            if self.original_max_position_embeddings <= 0:
+                raise ConfigError("rope_scaling.original_max_position_embeddings must be positive")
+            if not (self.beta_fast > 0 and self.beta_slow > 0):
+                raise ConfigError("rope_scaling.beta_fast and beta_slow must be positive")
         if self.kind == "llama3":
             if self.original_max_position_embeddings <= 0:
                 raise ConfigError("rope_scaling.original_max_position_embeddings must be positive")
@@ -106,6 +136,21 @@ def inverse_frequencies(rotary_dim: int, theta: float, scaling: RopeScaling) -> 
     if scaling.kind == "linear":
         s = 1.0 / float(np.float32(scaling.factor))
         return np.array([np.float32(float(f) * s) for f in inv], dtype=np.float32)
+    if scaling.kind == "yarn":
+        # all in 64-bit from the unrounded frequencies, rounded once
+        orig = float(scaling.original_max_position_embeddings)
+
+        def pair_of(turns: float) -> float:  # the (fractional) pair index that turns `turns` times over the original context
+            return rotary_dim * math.log(orig / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+
+        lo = max(math.floor(pair_of(scaling.beta_fast)), 0)
+        hi = min(math.ceil(pair_of(scaling.beta_slow)), rotary_dim - 1)
+        out = np.empty_like(inv)
+        for j in range(rotary_dim // 2):
+            f = base ** (-2.0 * j / rotary_dim)
+            ramp = min(max((j - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+            out[j] = np.float32(f / scaling.factor * ramp + f * (1.0 - ramp))
+        return out
     factor = float(np.float32(scaling.factor))
     lo = float(np.float32(scaling.low_freq_factor))
     hi = float(np.float32(scaling.high_freq_factor))
@@ -124,3 +169,10 @@ def inverse_frequencies(rotary_dim: int, theta: float, scaling: RopeScaling) -> 
             smooth = (orig / wavelen - lo) / (hi - lo)
             out[j] = np.float32((1.0 - smooth) * freq / factor + smooth * freq)
     return out
+
+
+def magnitude(scaling: RopeScaling) -> float:
+    """What cosines and sines are multiplied by: 0.1 ln(factor) + 1 for "yarn", else 1."""
+    if scaling.kind == "yarn":
+        return 0.1 * math.log(scaling.factor) + 1.0
+    return 1.0

@@ -397,3 +397,96 @@ RL_API int rl_swiglu(const void* gate_up, void* h, int act_dtype, int n_tokens, 
     RL_REFUSE(2, "swiglu: unknown dtype %d", act_dtype);
   RL_LAUNCH_RESULT();
 }
+
+// ---------------------------------------------------------------- gated activation with limits
+// h[t, i] = g' * sigmoid(alpha * g') * (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit),
+// g = gu[t, i], u = gu[t, ff + i]; in 32-bit.
+template <typename TA>
+__global__ void clamped_glu_kernel(const TA* __restrict__ gu, TA* __restrict__ h, int ff, long long total, float alpha, float limit) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long step = (long long)gridDim.x * blockDim.x;
+  for (; idx < total; idx += step) {
+    const long long t = idx / ff;
+    const int i = (int)(idx - t * ff);
+    const float g = fminf(to_f32(gu[t * 2 * ff + i]), limit);
+    const float u = fminf(fmaxf(to_f32(gu[t * 2 * ff + ff + i]), -limit), limit);
+    h[idx] = from_f32<TA>(g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f));
+  }
+}
+
+RL_API int rl_clamped_glu(const void* gate_up, void* h, int act_dtype, int n_tokens, int ff, float alpha, float limit, cudaStream_t stream) {
+  if (n_tokens <= 0 || ff <= 0) RL_REFUSE(1, "clamped_glu: n_tokens=%d ff=%d", n_tokens, ff);
+  const long long total = (long long)n_tokens * ff;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (act_dtype == RL_BF16)
+    clamped_glu_kernel<bf16><<<(int)blocks, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)h, ff, total, alpha, limit);
+  else if (act_dtype == RL_F32)
+    clamped_glu_kernel<float><<<(int)blocks, 256, 0, stream>>>((const float*)gate_up, (float*)h, ff, total, alpha, limit);
+  else
+    RL_REFUSE(2, "clamped_glu: unknown dtype %d", act_dtype);
+  RL_LAUNCH_RESULT();
+}
+
+// ---------------------------------------------------------------- a normed sublayer result, the residual sum, the next norm
+// For a layer that norms what its sublayer returns before adding it (and norms the stream again for the next sublayer):
+//   s = delta[0][t] + delta[1][t] + ...                         (32-bit, in this order)
+//   v = x[t] + s / sqrt(mean(s^2) + eps_d) * wd                 x[t] = v
+//   if w: out[t] = v / sqrt(mean(v^2) + eps) * w
+// One block per row, the row in shared memory between the passes; every sum in the block's fixed order.
+template <typename TA, typename TW, typename TD>
+__global__ void normed_add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_parts, long long part_stride,
+                                          const TW* __restrict__ wd, float eps_d, const TW* __restrict__ w, float eps,
+                                          TA* __restrict__ out, const int* __restrict__ rows, int d, int write_x) {
+  extern __shared__ __align__(16) float row[];
+  __shared__ float red[32];
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int t = rows ? rows[r] : r;
+  float* xr = x + (size_t)t * d;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float s = 0.f;
+    for (int p = 0; p < n_parts; ++p) s += to_f32(delta[(size_t)p * part_stride + (size_t)t * d + i]);
+    row[i] = s;
+    ss += s * s;
+  }
+  const float inv_d = 1.0f / sqrtf(block_sum(ss, red) / (float)d + eps_d);
+  ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float v = xr[i] + row[i] * inv_d * to_f32(wd[i]);
+    row[i] = v;
+    if (write_x) xr[i] = v;
+    ss += v * v;
+  }
+  if (w == nullptr) return;
+  const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)d + eps);
+  TA* o = out + (size_t)r * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_f32<TA>(row[i] * inv * to_f32(w[i]));
+}
+
+RL_API int rl_normed_add_rmsnorm(float* x, const void* delta, int delta_dtype, int n_parts, long long part_stride, const void* wd,
+                                 float eps_d, const void* w, int w_dtype, float eps, void* out, int act_dtype, const int* rows,
+                                 int n_rows, int d, int write_x, cudaStream_t stream) {
+  if (n_rows <= 0 || d <= 0 || n_parts <= 0 || delta == nullptr || wd == nullptr)
+    RL_REFUSE(1, "normed_add_rmsnorm: n_rows=%d d=%d n_parts=%d", n_rows, d, n_parts);
+  if (w != nullptr && out == nullptr) RL_REFUSE(2, "normed_add_rmsnorm: a weight but no output");
+  const size_t smem = (size_t)d * sizeof(float);
+  if (smem > 48 * 1024) RL_REFUSE(3, "normed_add_rmsnorm: a row of %d values does not fit shared memory", d);
+  int th = ((d + 31) / 32) * 32;
+  th = th > 512 ? 512 : th;
+#define RL_NN(TA, TW, TD)                                                                                                       \
+  do {                                                                                                                          \
+    RL_LAUNCH_CHECK(rl_launch<false>(normed_add_rmsnorm_kernel<TA, TW, TD>, n_rows, th, smem, stream, x, (const TD*)delta, n_parts, \
+                                     part_stride, (const TW*)wd, eps_d, (const TW*)w, eps, (TA*)out, rows, d, write_x));        \
+    return 0;                                                                                                                   \
+  } while (0)
+  if (act_dtype == RL_BF16 && w_dtype == RL_BF16 && delta_dtype == RL_BF16) RL_NN(bf16, bf16, bf16);
+  if (act_dtype == RL_BF16 && w_dtype == RL_BF16 && delta_dtype == RL_F32) RL_NN(bf16, bf16, float);
+  if (act_dtype == RL_BF16 && w_dtype == RL_F32 && delta_dtype == RL_BF16) RL_NN(bf16, float, bf16);
+  if (act_dtype == RL_BF16 && w_dtype == RL_F32 && delta_dtype == RL_F32) RL_NN(bf16, float, float);
+  if (act_dtype == RL_F32 && w_dtype == RL_F32 && delta_dtype == RL_F32) RL_NN(float, float, float);
+#undef RL_NN
+  RL_REFUSE(5, "normed_add_rmsnorm: unsupported dtypes act=%d w=%d delta=%d", act_dtype, w_dtype, delta_dtype);
+}

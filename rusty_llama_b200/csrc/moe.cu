@@ -1,0 +1,292 @@
+// A routed feed-forward: every token is sent to `top` of E small gated feed-forwards.
+//
+//   moe_router   z = W_r x in 32-bit, s = softmax(z) over all experts; the `top` experts with the largest
+//                s + bias are chosen (ties to the lower index), their weights are their s (optionally divided by
+//                their sum); one more row of W_r, if present, gives a per-token gate sigmoid(w_g . x)
+//   moe_plan     counts the (token, choice) pairs of each expert, lays them out expert after expert (`order`,
+//                with the inverse `place`), and cuts each expert's range into row tiles (`tiles`)
+//   moe_gemm     one kernel for all experts: a block takes one row tile (rows of ONE expert) and one column
+//                tile; rows are gathered through `order`; with ACT the block computes the gate and the up
+//                product together and writes act(gate) * up
+//   moe_combine  out[t] = sum_j weight[t,j] * y[place[t,j]]  (+ gate[t] * shared[t]), in the order j = 0, 1, ...
+//
+// Nothing here depends on the host knowing how many tokens an expert got: grids are sized by upper bounds and
+// blocks without work leave, so a step with these kernels can be captured in a CUDA graph.  Each output is one
+// running 32-bit sum over ascending k, whatever the tile it lies in: a token's result does not depend on what
+// else is in the batch.
+#include "common.cuh"
+
+RL_DEFINE_ERROR_TEXT()
+
+#define MOE_TM 32  // rows of a tile: the (token, choice) pairs of one expert, 32 at a time
+#define MOE_TN 64
+#define MOE_TK 16
+
+// ---------------------------------------------------------------- router
+// One block of 128 threads per token.  w: float32 [E (+1), d]; x in the activation type.
+template <typename T>
+__global__ void moe_router_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ w, const float* __restrict__ bias,
+                                  int E, int d, int top, int renorm, int has_gate, int* __restrict__ ids,
+                                  float* __restrict__ weights, float* __restrict__ gate) {
+  extern __shared__ float z[];  // E + 1 logits, then E choice scores
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const T* xr = x + (size_t)t * ldx;
+  const int rows = E + (has_gate ? 1 : 0);
+  for (int e = warp; e < rows; e += nwarps) {
+    const float* wr = w + (size_t)e * d;
+    float s = 0.f;
+    for (int k = lane; k < d; k += 32) s += to_f32(xr[k]) * wr[k];
+    s = warp_sum(s);
+    if (lane == 0) z[e] = s;
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  float* choice = z + E + 1;
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) sum += expf(z[e] - mx);
+  sum = warp_sum(sum);
+  for (int e = lane; e < E; e += 32) {
+    const float s = expf(z[e] - mx) / sum;
+    z[e] = s;
+    choice[e] = s + (bias ? bias[e] : 0.f);
+  }
+  __syncwarp();
+  float chosen_sum = 0.f;
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int e = lane; e < E; e += 32)
+      if (choice[e] > best) {  // ascending e within a lane: the lower index keeps a tie
+        best = choice[e];
+        at = e;
+      }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ob > best || (ob == best && oa < at)) {
+        best = ob;
+        at = oa;
+      }
+    }
+    if (lane == 0) {
+      ids[(size_t)t * top + j] = at;
+      weights[(size_t)t * top + j] = z[at];
+      choice[at] = -INFINITY;
+    }
+    chosen_sum += z[at];
+    __syncwarp();
+  }
+  if (renorm && lane == 0)
+    for (int j = 0; j < top; ++j) weights[(size_t)t * top + j] /= chosen_sum;
+  if (has_gate && lane == 0) gate[t] = 1.0f / (1.0f + expf(-z[E]));
+}
+
+RL_API int rl_moe_router(const void* x, int ldx, int dtype, const float* w, const float* bias, int n_tokens, int E, int d,
+                         int top, int renorm, int has_gate, int* ids, float* weights, float* gate, cudaStream_t stream) {
+  if (n_tokens <= 0 || E <= 0 || d <= 0 || top <= 0 || top > E) RL_REFUSE(1, "moe_router: T=%d E=%d d=%d top=%d", n_tokens, E, d, top);
+  if (has_gate && gate == nullptr) RL_REFUSE(2, "moe_router: a gate row but nowhere to write the gate");
+  const size_t smem = (size_t)(2 * E + 2) * sizeof(float);
+  if (smem > 48 * 1024) RL_REFUSE(3, "moe_router: %d experts exceed the kernel's shared memory", E);
+  if (dtype == RL_BF16)
+    RL_LAUNCH_CHECK(rl_launch<false>(moe_router_kernel<bf16>, n_tokens, 128, smem, stream, (const bf16*)x, ldx, w, bias, E, d, top,
+                                     renorm, has_gate, ids, weights, gate));
+  else if (dtype == RL_F32)
+    RL_LAUNCH_CHECK(rl_launch<false>(moe_router_kernel<float>, n_tokens, 128, smem, stream, (const float*)x, ldx, w, bias, E, d,
+                                     top, renorm, has_gate, ids, weights, gate));
+  else
+    RL_REFUSE(4, "moe_router: unknown dtype %d", dtype);
+  return 0;
+}
+
+// ---------------------------------------------------------------- plan
+// ids[n] (n = T * top pairs) -> order[n] (pairs laid out expert after expert, each expert's pairs in ascending
+// pair index), place[pair] (its row in that layout), tiles[1 + 3 * max_tiles]: the number of tiles, then
+// (expert, first row, rows) per tile.  One block; E counters in shared memory.
+__global__ void moe_plan_kernel(const int* __restrict__ ids, int n, int E, int* __restrict__ order, int* __restrict__ place,
+                                int* __restrict__ tiles) {
+  extern __shared__ int cnt[];  // E counts, then E + 1 offsets
+  pdl_trigger();
+  pdl_wait();
+  int* off = cnt + E;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) atomicAdd(&cnt[ids[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0, nt = 0;
+    for (int e = 0; e < E; ++e) {
+      off[e] = at;
+      for (int r = 0; r < cnt[e]; r += MOE_TM) {
+        tiles[1 + 3 * nt] = e;
+        tiles[2 + 3 * nt] = at + r;
+        tiles[3 + 3 * nt] = min(MOE_TM, cnt[e] - r);
+        ++nt;
+      }
+      at += cnt[e];
+    }
+    off[E] = at;
+    tiles[0] = nt;
+  }
+  __syncthreads();
+  // a pair's row: its expert's offset plus the number of earlier pairs of the same expert.  One warp per
+  // expert walks the pairs in order, so the layout is the same on every run.
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int e = warp; e < E; e += nwarps) {
+    int at = off[e];
+    for (int base = 0; base < n; base += 32) {
+      const int i = base + lane;
+      const bool mine = i < n && ids[i] == e;
+      const unsigned m = __ballot_sync(0xffffffffu, mine);
+      if (mine) {
+        const int r = at + __popc(m & ((1u << lane) - 1u));
+        order[r] = i;
+        place[i] = r;
+      }
+      at += __popc(m);
+    }
+  }
+}
+
+RL_API int rl_moe_tile_rows() { return MOE_TM; }
+
+RL_API int rl_moe_plan(const int* ids, int n, int E, int* order, int* place, int* tiles, cudaStream_t stream) {
+  if (n <= 0 || E <= 0) RL_REFUSE(1, "moe_plan: n=%d E=%d", n, E);
+  const size_t smem = (size_t)(2 * E + 1) * sizeof(int);
+  if (smem > 48 * 1024) RL_REFUSE(2, "moe_plan: %d experts exceed the kernel's shared memory", E);
+  RL_LAUNCH_CHECK(rl_launch<false>(moe_plan_kernel, 1, 1024, smem, stream, ids, n, E, order, place, tiles));
+  return 0;
+}
+
+// ---------------------------------------------------------------- all experts' products in one launch
+// Row r of the layout belongs to pair order[r]; its input row is x[order[r] / gather_div] when `order` is given
+// (the token's activations), else x[r].  w: [E, N, K]; with ACT also w2: [E, N, K] and out = silu(x w^T) * (x w2^T).
+// blockIdx.y walks the tiles of the plan; a block beyond the plan's count leaves.
+template <typename TA, typename TO, bool ACT>
+__global__ void __launch_bounds__(256)
+moe_gemm_kernel(const TA* __restrict__ x, int ldx, const int* __restrict__ order, int gather_div, const TA* __restrict__ w,
+                const TA* __restrict__ w2, TO* __restrict__ out, int ldo, const int* __restrict__ tiles, int N, int K) {
+  __shared__ float xs[MOE_TK][MOE_TM + 4];
+  __shared__ float ws[MOE_TK][MOE_TN + 4];
+  __shared__ float ws2[ACT ? MOE_TK : 1][MOE_TN + 4];
+  __shared__ int src[MOE_TM];
+  pdl_trigger();
+  pdl_wait();
+  if ((int)blockIdx.y >= tiles[0]) return;
+  const int e = tiles[1 + 3 * blockIdx.y], r0 = tiles[2 + 3 * blockIdx.y], rows = tiles[3 + 3 * blockIdx.y];
+  const int tid = threadIdx.x, n0 = blockIdx.x * MOE_TN;
+  const int ty = tid / 16, tx = tid % 16;  // 16 x 16 threads: 2 rows x 4 columns each
+  if (tid < MOE_TM) src[tid] = tid < rows ? (order ? order[r0 + tid] / gather_div : r0 + tid) : -1;
+  __syncthreads();
+  const TA* we = w + (size_t)e * N * K;
+  const TA* we2 = ACT ? w2 + (size_t)e * N * K : nullptr;
+  float acc[2][4], acc2[2][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = acc2[i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += MOE_TK) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int idx = tid + i * 256;
+      const int r = idx / MOE_TK, c = idx % MOE_TK;
+      const int k = k0 + c;
+      xs[c][r] = (src[r] >= 0 && k < K) ? to_f32(x[(size_t)src[r] * ldx + k]) : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = tid + i * 256;
+      const int r = idx / MOE_TK, c = idx % MOE_TK;
+      const int k = k0 + c;
+      const bool in = n0 + r < N && k < K;
+      ws[c][r] = in ? to_f32(we[(size_t)(n0 + r) * K + k]) : 0.f;
+      if (ACT) ws2[c][r] = in ? to_f32(we2[(size_t)(n0 + r) * K + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int c = 0; c < MOE_TK; ++c) {
+      float a[2], b[4], b2[4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) a[i] = xs[c][ty * 2 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        b[j] = ws[c][tx * 4 + j];
+        if (ACT) b2[j] = ws2[c][tx * 4 + j];
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+          if (ACT) acc2[i][j] = fmaf(a[i], b2[j], acc2[i][j]);
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = ty * 2 + i;
+    if (r >= rows) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= N) continue;
+      float v = acc[i][j];
+      if (ACT) v = v * (1.0f / (1.0f + expf(-v))) * acc2[i][j];
+      out[(size_t)(r0 + r) * ldo + n] = from_f32<TO>(v);
+    }
+  }
+}
+
+RL_API int rl_moe_gemm(const void* x, int ldx, int dtype, const int* order, int gather_div, const void* w, const void* w2,
+                       void* out, int out_dtype, int ldo, const int* tiles, int max_tiles, int N, int K, cudaStream_t stream) {
+  if (max_tiles <= 0 || N <= 0 || K <= 0 || gather_div <= 0) RL_REFUSE(1, "moe_gemm: tiles=%d N=%d K=%d div=%d", max_tiles, N, K, gather_div);
+  if (max_tiles > 65535) RL_REFUSE(2, "moe_gemm: %d row tiles exceed the grid", max_tiles);
+  dim3 grid((N + MOE_TN - 1) / MOE_TN, max_tiles);
+#define RL_MG(TA, TO, ACT)                                                                                                  \
+  RL_LAUNCH_CHECK(rl_launch<false>(moe_gemm_kernel<TA, TO, ACT>, grid, 256, 0, stream, (const TA*)x, ldx, order, gather_div, \
+                                   (const TA*)w, (const TA*)w2, (TO*)out, ldo, tiles, N, K))
+  if (dtype == RL_BF16 && out_dtype == RL_BF16 && w2) RL_MG(bf16, bf16, true);
+  else if (dtype == RL_BF16 && out_dtype == RL_BF16) RL_MG(bf16, bf16, false);
+  else if (dtype == RL_BF16 && out_dtype == RL_F32 && !w2) RL_MG(bf16, float, false);
+  else if (dtype == RL_F32 && out_dtype == RL_F32 && w2) RL_MG(float, float, true);
+  else if (dtype == RL_F32 && out_dtype == RL_F32) RL_MG(float, float, false);
+  else RL_REFUSE(3, "moe_gemm: unsupported types in=%d out=%d act=%d", dtype, out_dtype, w2 != nullptr);
+#undef RL_MG
+  return 0;
+}
+
+// ---------------------------------------------------------------- weighted sum of a token's experts
+// out[t, :] = sum_j weights[t, j] * y[place[t * top + j], :]  (+ gate[t] * shared[t, :]); y is float32.
+template <typename TS, typename TO>
+__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place, const float* __restrict__ weights,
+                                   int top, const TS* __restrict__ shared, const float* __restrict__ gate, TO* __restrict__ out, int d) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float v = 0.f;
+    for (int j = 0; j < top; ++j) v += weights[(size_t)t * top + j] * y[(size_t)place[(size_t)t * top + j] * d + i];
+    if (shared) v += (gate ? gate[t] : 1.f) * to_f32(shared[(size_t)t * d + i]);
+    out[(size_t)t * d + i] = from_f32<TO>(v);
+  }
+}
+
+RL_API int rl_moe_combine(const float* y, const int* place, const float* weights, int top, const void* shared, int shared_dtype,
+                          const float* gate, void* out, int out_dtype, int n_tokens, int d, cudaStream_t stream) {
+  if (n_tokens <= 0 || d <= 0 || top <= 0) RL_REFUSE(1, "moe_combine: T=%d d=%d top=%d", n_tokens, d, top);
+#define RL_MC(TS, TO)                                                                                                          \
+  RL_LAUNCH_CHECK(rl_launch<false>(moe_combine_kernel<TS, TO>, n_tokens, 256, 0, stream, y, place, weights, top, (const TS*)shared, \
+                                   gate, (TO*)out, d))
+  if (shared_dtype == RL_BF16 && out_dtype == RL_F32) RL_MC(bf16, float);
+  else if (shared_dtype == RL_F32 && out_dtype == RL_F32) RL_MC(float, float);
+  else if (shared_dtype == RL_BF16 && out_dtype == RL_BF16) RL_MC(bf16, bf16);
+  else RL_REFUSE(2, "moe_combine: unsupported types shared=%d out=%d", shared_dtype, out_dtype);
+#undef RL_MC
+  return 0;
+}

@@ -869,3 +869,262 @@ def sample_chain(
     )
     _check(lib, rc, "sample_chain")
     return out
+
+
+# ------------------------------------------------------------------ sublayer results that are normed before they are added
+def normed_add_rmsnorm(
+    x: torch.Tensor, delta: torch.Tensor, delta_weight: torch.Tensor, delta_eps: float, weight: Optional[torch.Tensor], eps: float,
+    act_dtype: torch.dtype, rows: Optional[torch.Tensor] = None, write_x: bool = True,
+) -> Optional[torch.Tensor]:
+    """x (float32 [T, d]) += rmsnorm(sum of delta parts) * delta_weight; returns rmsnorm(x) * weight in `act_dtype`
+    (None without a weight).  delta: [T, d] or [parts, T, d], in `act_dtype` or float32.  Both norm weights have one type."""
+    _cuda(x, "normed_add_rmsnorm x", torch.float32)
+    T, d = x.shape
+    _cuda(delta, "normed_add_rmsnorm delta")
+    _need(delta.dtype in (act_dtype, torch.float32), f"normed_add_rmsnorm: delta is {delta.dtype} in a run of {act_dtype}")
+    if delta.dim() == 2:
+        _need(tuple(delta.shape) == (T, d), f"normed_add_rmsnorm: delta {tuple(delta.shape)} does not match x {(T, d)}")
+        n_parts, part_stride = 1, 0
+    else:
+        _need(delta.dim() == 3 and tuple(delta.shape[1:]) == (T, d), f"normed_add_rmsnorm: delta {tuple(delta.shape)} does not match x {(T, d)}")
+        n_parts, part_stride = delta.shape[0], T * d
+    _cuda(delta_weight, "normed_add_rmsnorm delta_weight")
+    _need(tuple(delta_weight.shape) == (d,), "normed_add_rmsnorm: delta_weight does not match d")
+    n_rows = T if rows is None else rows.numel()
+    out = None
+    if weight is not None:
+        _cuda(weight, "normed_add_rmsnorm weight", delta_weight.dtype)
+        _need(tuple(weight.shape) == (d,), "normed_add_rmsnorm: weight does not match d")
+        out = torch.empty((n_rows, d), dtype=act_dtype, device=x.device)
+    if rows is not None:
+        _cuda(rows, "normed_add_rmsnorm rows", torch.int32)
+    if n_rows == 0:
+        return out
+    lib = build.load("elementwise")
+    rc = lib.rl_normed_add_rmsnorm(
+        _p(x), _p(delta), c_int(_DT[delta.dtype]), c_int(n_parts), c_ll(part_stride), _p(delta_weight), c_float(delta_eps), _p(weight),
+        c_int(_dt(delta_weight, "normed_add_rmsnorm weight")), c_float(eps), _p(out), c_int(_DT[act_dtype]), _p(rows), c_int(n_rows),
+        c_int(d), c_int(1 if write_x else 0), _stream(),
+    )
+    _check(lib, rc, "normed_add_rmsnorm")
+    return out
+
+
+def clamped_glu(gate_up: torch.Tensor, alpha: float, limit: float) -> torch.Tensor:
+    """h[t, i] = g * sigmoid(alpha * g) * (u + 1), g = min(gate_up[t, i], limit), u = clamp(gate_up[t, ff + i], -limit, limit)."""
+    _cuda(gate_up, "clamped_glu input")
+    _need(gate_up.dim() == 2 and gate_up.shape[1] % 2 == 0, "clamped_glu: input must be [T, 2*ff]")
+    T, ff = gate_up.shape[0], gate_up.shape[1] // 2
+    out = torch.empty((T, ff), dtype=gate_up.dtype, device=gate_up.device)
+    lib = build.load("elementwise")
+    rc = lib.rl_clamped_glu(_p(gate_up), _p(out), c_int(_dt(gate_up, "clamped_glu")), c_int(T), c_int(ff), c_float(alpha), c_float(limit), _stream())
+    _check(lib, rc, "clamped_glu")
+    return out
+
+
+# ------------------------------------------------------------------ latent attention
+def latent_prep(
+    q: torch.Tensor, kv: Optional[torch.Tensor], norm_w: Optional[torch.Tensor], eps: float, freq: Optional[torch.Tensor], n_pairs: int,
+    magnitude: float, tok_pos: torch.Tensor, tok_seq: torch.Tensor, block_table: Optional[torch.Tensor], pages: Optional[torch.Tensor],
+    q_cat: torch.Tensor, num_heads: int, dim: int, rot: int, rank: int,
+) -> None:
+    """Per token: kv's first `rank` values RMS-normed (weight norm_w) and its last `rot` values rotated go into the token's
+    place in `pages` [pages, 1, PAGE_SIZE, rank + rot] (kv None: nothing is stored); the rotated part of every head of
+    q [T, >= H (dim + rot)] is rotated into q_cat[T, H, rank:]."""
+    _cuda(q, "latent_prep q", contiguous=False)
+    ldq = _rows(q, "latent_prep q")
+    T = q.shape[0]
+    _need(q.shape[1] >= num_heads * (dim + rot), "latent_prep: q rows too short")
+    _cuda(q_cat, "latent_prep q_cat", q.dtype)
+    _need(tuple(q_cat.shape) == (T, num_heads, rank + rot), "latent_prep: q_cat has the wrong shape")
+    _cuda(tok_pos, "latent_prep tok_pos", torch.int32)
+    _cuda(tok_seq, "latent_prep tok_seq", torch.int32)
+    _need(tok_pos.numel() == T and tok_seq.numel() == T, "latent_prep: one position and one sequence index per token")
+    ldkv, width = 0, 0
+    if kv is not None:
+        _cuda(kv, "latent_prep kv", q.dtype, contiguous=False)
+        ldkv = _rows(kv, "latent_prep kv")
+        _need(kv.shape[0] == T and kv.shape[1] >= rank + rot, "latent_prep: kv rows do not fit")
+        _cuda(pages, "latent_prep pages", q.dtype)
+        _need(pages.dim() == 4 and tuple(pages.shape[1:]) == (1, PAGE_SIZE, rank + rot), f"latent_prep: pages {tuple(pages.shape)}")
+        _cuda(block_table, "latent_prep block_table", torch.int32)
+        _need(block_table.dim() == 2, "latent_prep: block_table must be [S, width]")
+        width = block_table.shape[1]
+        _cuda(norm_w, "latent_prep norm_w", torch.float32)
+        _need(norm_w.numel() == rank, "latent_prep: norm weight does not match the latent size")
+    if n_pairs:
+        _cuda(freq, "latent_prep freq", torch.float32)
+        _need(freq.numel() >= n_pairs, "latent_prep: too few angles")
+    lib = build.load("latent_attention")
+    rc = lib.rl_latent_prep(
+        _p(q), c_int(ldq), _p(kv), c_int(ldkv), c_int(_dt(q, "latent_prep")), _p(norm_w), c_float(eps), _p(freq), c_int(n_pairs),
+        c_float(magnitude), _p(tok_pos), _p(tok_seq), _p(block_table) if kv is not None else c_void_p(0), c_int(width),
+        _p(pages) if kv is not None else c_void_p(0), c_int(PAGE_SIZE), _p(q_cat), c_int(T), c_int(num_heads), c_int(dim), c_int(rot),
+        c_int(rank), _stream(),
+    )
+    _check(lib, rc, "latent_prep")
+
+
+def head_linear(
+    x: torch.Tensor, x_head_stride: int, w: torch.Tensor, out: torch.Tensor, out_head_stride: int,
+    gate: Optional[torch.Tensor] = None, gate_head_stride: int = 0,
+) -> torch.Tensor:
+    """out[t, h, n] = sum_k x[t, h, k] * w[h, n, k] (optionally times sigmoid(gate[t, h, n])), one small product per head.
+
+    x, out, gate: 2-D [T, row] tensors with dense rows; head h's values start `*_head_stride` * h into a row.  w: [H, N, K]."""
+    _cuda(x, "head_linear x", contiguous=False)
+    _cuda(w, "head_linear w", x.dtype)
+    _cuda(out, "head_linear out", x.dtype, contiguous=False)
+    _need(w.dim() == 3, "head_linear: w must be [H, N, K]")
+    H, N, K = w.shape
+    M = x.shape[0]
+    ldx, ldo = _rows(x, "head_linear x"), _rows(out, "head_linear out")
+    _need(out.shape[0] == M, "head_linear: x and out have different row counts")
+    _need((H - 1) * x_head_stride + K <= x.shape[1] and (H - 1) * out_head_stride + N <= out.shape[1], "head_linear: rows too short for the heads")
+    ldg = 0
+    if gate is not None:
+        _cuda(gate, "head_linear gate", x.dtype, contiguous=False)
+        ldg = _rows(gate, "head_linear gate")
+        _need(gate.shape[0] == M and (H - 1) * gate_head_stride + N <= gate.shape[1], "head_linear: gate rows do not fit")
+    lib = build.load("latent_attention")
+    rc = lib.rl_head_linear(
+        _p(x), c_int(ldx), c_int(x_head_stride), _p(w), c_ll(N * K), c_int(K), c_int(1), _p(out), c_int(ldo), c_int(out_head_stride),
+        _p(gate), c_int(ldg), c_int(gate_head_stride), c_int(_dt(x, "head_linear")), c_int(M), c_int(H), c_int(N), c_int(K), _stream(),
+    )
+    _check(lib, rc, "head_linear")
+    return out
+
+
+def latent_attn(
+    q_cat: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor, tok_seq: torch.Tensor, tok_pos: torch.Tensor,
+    sink: Optional[torch.Tensor], rank: int, rot: int, scale: float, window: int = 0, out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Attention of each token's heads q_cat[T, H, rank + rot] over its sequence's cached rows 0..pos of
+    pages [pages, 1, PAGE_SIZE, rank + rot]; softmax with a sink per head (float32 [H], or None); returns the
+    probability-weighted sums of the rows' first `rank` values, [T, H, rank]."""
+    _cuda(q_cat, "latent_attn q_cat")
+    _need(q_cat.dim() == 3 and q_cat.shape[2] == rank + rot, "latent_attn: q_cat must be [T, H, rank + rot]")
+    T, H = q_cat.shape[0], q_cat.shape[1]
+    _cuda(pages, "latent_attn pages", q_cat.dtype)
+    _need(pages.dim() == 4 and tuple(pages.shape[1:]) == (1, PAGE_SIZE, rank + rot), f"latent_attn: pages {tuple(pages.shape)}")
+    _cuda(block_table, "latent_attn block_table", torch.int32)
+    _cuda(tok_seq, "latent_attn tok_seq", torch.int32)
+    _cuda(tok_pos, "latent_attn tok_pos", torch.int32)
+    _need(tok_seq.numel() == T and tok_pos.numel() == T and block_table.dim() == 2, "latent_attn: metadata sizes")
+    if sink is not None:
+        _cuda(sink, "latent_attn sink", torch.float32)
+        _need(sink.numel() == H, "latent_attn: one sink per head")
+    if out is None:
+        out = torch.empty((T, H, rank), dtype=q_cat.dtype, device=q_cat.device)
+    _cuda(out, "latent_attn out", q_cat.dtype)
+    _need(tuple(out.shape) == (T, H, rank), "latent_attn: out has the wrong shape")
+    lib = build.load("latent_attention")
+    rc = lib.rl_latent_attn(
+        _p(q_cat), _p(pages), c_int(_dt(q_cat, "latent_attn")), _p(block_table), c_int(block_table.shape[1]), _p(tok_seq), _p(tok_pos),
+        _p(sink), _p(out), c_int(T), c_int(H), c_int(rank), c_int(rot), c_int(PAGE_SIZE), c_int(window), c_float(scale), _stream(),
+    )
+    _check(lib, rc, "latent_attn")
+    return out
+
+
+# ------------------------------------------------------------------ routed feed-forward
+def moe_tile_rows() -> int:
+    return int(build.load("moe").rl_moe_tile_rows())
+
+
+def moe_router(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], n_experts: int, top: int, renormalize: bool = False):
+    """x[T, d], w float32 [E (+1), d] -> (ids int32 [T, top], weights float32 [T, top], gate float32 [T] or None).
+
+    Softmax over the E experts in 32-bit; the `top` largest of score + bias are chosen, their weights are their scores
+    (divided by their sum if `renormalize`).  A row E of w gives gate = sigmoid(w[E] . x)."""
+    _cuda(x, "moe_router x", contiguous=False)
+    _cuda(w, "moe_router w", torch.float32)
+    T, d = x.shape
+    has_gate = w.shape[0] == n_experts + 1
+    _need(w.dim() == 2 and w.shape[1] == d and w.shape[0] in (n_experts, n_experts + 1), f"moe_router: w {tuple(w.shape)} for {n_experts} experts of width {d}")
+    if bias is not None:
+        _cuda(bias, "moe_router bias", torch.float32)
+        _need(bias.numel() == n_experts, "moe_router: one bias per expert")
+    ids = torch.empty((T, top), dtype=torch.int32, device=x.device)
+    weights = torch.empty((T, top), dtype=torch.float32, device=x.device)
+    gate = torch.empty((T,), dtype=torch.float32, device=x.device) if has_gate else None
+    lib = build.load("moe")
+    rc = lib.rl_moe_router(
+        _p(x), c_int(_rows(x, "moe_router x")), c_int(_dt(x, "moe_router")), _p(w), _p(bias), c_int(T), c_int(n_experts), c_int(d), c_int(top),
+        c_int(1 if renormalize else 0), c_int(1 if has_gate else 0), _p(ids), _p(weights), _p(gate), _stream(),
+    )
+    _check(lib, rc, "moe_router")
+    return ids, weights, gate
+
+
+def moe_max_tiles(n_pairs: int, n_experts: int) -> int:
+    """Upper bound of the row tiles that `moe_plan` makes of n_pairs (token, choice) pairs."""
+    rows = moe_tile_rows()
+    return min(n_pairs, n_pairs // rows + n_experts)
+
+
+def moe_plan(ids: torch.Tensor, n_experts: int):
+    """ids int32 [T, top] -> (order [T top], place [T top], tiles [1 + 3 max_tiles], max_tiles), all on the device."""
+    _cuda(ids, "moe_plan ids", torch.int32)
+    n = ids.numel()
+    max_tiles = moe_max_tiles(n, n_experts)
+    order = torch.empty((n,), dtype=torch.int32, device=ids.device)
+    place = torch.empty((n,), dtype=torch.int32, device=ids.device)
+    tiles = torch.empty((1 + 3 * max_tiles,), dtype=torch.int32, device=ids.device)
+    lib = build.load("moe")
+    rc = lib.rl_moe_plan(_p(ids), c_int(n), c_int(n_experts), _p(order), _p(place), _p(tiles), _stream())
+    _check(lib, rc, "moe_plan")
+    return order, place, tiles, max_tiles
+
+
+def moe_gemm(
+    x: torch.Tensor, w: torch.Tensor, tiles: torch.Tensor, max_tiles: int, n_rows: int, order: Optional[torch.Tensor] = None,
+    gather_div: int = 1, w2: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+) -> torch.Tensor:
+    """out[r] = w[expert of r] . x[row of r] for the n_rows rows of a plan's layout; w: [E, N, K].
+
+    order given: row r reads x[order[r] // gather_div], else x[r].  w2 given: out = silu(w x) * (w2 x)."""
+    _cuda(x, "moe_gemm x", contiguous=False)
+    _cuda(w, "moe_gemm w", x.dtype)
+    _need(w.dim() == 3 and w.shape[2] == x.shape[1], f"moe_gemm: w {tuple(w.shape)} against x {tuple(x.shape)}")
+    E, N, K = w.shape
+    if w2 is not None:
+        _cuda(w2, "moe_gemm w2", x.dtype)
+        _need(tuple(w2.shape) == (E, N, K), "moe_gemm: w2 does not match w")
+    out_dtype = out_dtype or x.dtype
+    out = torch.empty((n_rows, N), dtype=out_dtype, device=x.device)
+    lib = build.load("moe")
+    rc = lib.rl_moe_gemm(
+        _p(x), c_int(_rows(x, "moe_gemm x")), c_int(_dt(x, "moe_gemm")), _p(order), c_int(gather_div), _p(w), _p(w2), _p(out),
+        c_int(_dt(out, "moe_gemm out")), c_int(N), _p(tiles), c_int(max_tiles), c_int(N), c_int(K), _stream(),
+    )
+    _check(lib, rc, "moe_gemm")
+    return out
+
+
+def moe_combine(
+    y: torch.Tensor, place: torch.Tensor, weights: torch.Tensor, shared: Optional[torch.Tensor], gate: Optional[torch.Tensor],
+    out_dtype: torch.dtype = torch.float32,
+) -> torch.Tensor:
+    """out[t] = sum_j weights[t, j] * y[place[t, j]] (+ gate[t] * shared[t]); y float32 [T top, d]."""
+    _cuda(y, "moe_combine y", torch.float32)
+    _cuda(weights, "moe_combine weights", torch.float32)
+    _cuda(place, "moe_combine place", torch.int32)
+    T, top = weights.shape
+    d = y.shape[1]
+    _need(y.shape[0] == T * top and place.numel() == T * top, "moe_combine: sizes do not fit")
+    shared_dt = _F32
+    if shared is not None:
+        _cuda(shared, "moe_combine shared")
+        _need(tuple(shared.shape) == (T, d), "moe_combine: shared has the wrong shape")
+        shared_dt = _dt(shared, "moe_combine shared")
+    if gate is not None:
+        _cuda(gate, "moe_combine gate", torch.float32)
+    out = torch.empty((T, d), dtype=out_dtype, device=y.device)
+    lib = build.load("moe")
+    rc = lib.rl_moe_combine(
+        _p(y), _p(place), _p(weights), c_int(top), _p(shared), c_int(shared_dt), _p(gate), _p(out), c_int(_dt(out, "moe_combine out")),
+        c_int(T), c_int(d), _stream(),
+    )
+    _check(lib, rc, "moe_combine")
+    return out

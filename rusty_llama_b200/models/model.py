@@ -28,7 +28,8 @@ class Model:
         self.blocks = []
         for layer in spec.layers:
             mixer = MIXERS.build(layer.mixer, runtime)
-            ff = FEED_FORWARDS.build(layer.feed_forward, runtime)
+            # a layer may have no feed-forward at all
+            ff = None if layer.feed_forward is None else FEED_FORWARDS.build(layer.feed_forward, runtime)
             norms = {name: NORMS.build(n, runtime) for name, n in layer.norms.items()}
             self.blocks.append(BLOCKS.build(PartSpec(layer.block), runtime, mixer, ff, norms))
         self.final_norm = NORMS.build(spec.final_norm, runtime)
@@ -47,7 +48,8 @@ class Model:
         yield from walk(self.embedding)
         for b in self.blocks:
             yield from walk(b.mixer)
-            yield from walk(b.feed_forward)
+            if b.feed_forward is not None:
+                yield from walk(b.feed_forward)
             for n in b.norms.values():
                 yield from walk(n)
         yield from walk(self.final_norm)
@@ -88,7 +90,7 @@ class Model:
         for _, need in self.cache_needs():
             if isinstance(need, KVNeed):
                 size = torch.empty((), dtype=need.dtype or self.rt.dtype).element_size()
-                total += 2 * need.num_kv_heads * need.head_dim * size
+                total += (2 if need.values else 1) * need.num_kv_heads * need.head_dim * size
         return total
 
     def new_cache(self, max_tokens: int, max_seqs: int) -> Cache:

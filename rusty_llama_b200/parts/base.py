@@ -89,7 +89,9 @@ class ParamInfo:
 
     kind "matrix": stored in the run's matrix type (bfloat16, or float32 on the
     32-bit path).  kind "vector": a tensor stored in 32-bit stays so; otherwise
-    it follows the run.  kind "table": integers, kept as int32."""
+    it follows the run.  kind "scalars": a few learned numbers that enter 32-bit
+    arithmetic directly (a softmax sink, a router's bias, a router's rows): always
+    float32 at run time.  kind "table": integers, kept as int32."""
 
     shape: Tuple[int, ...]
     kind: str = "matrix"
@@ -98,6 +100,8 @@ class ParamInfo:
 def runtime_dtype(info: ParamInfo, stored: torch.dtype, run: torch.dtype) -> torch.dtype:
     if info.kind == "table":
         return torch.int32
+    if info.kind == "scalars":
+        return torch.float32
     if info.kind == "vector":
         return torch.float32 if (stored == torch.float32 or run == torch.float32) else run
     return run
@@ -106,12 +110,16 @@ def runtime_dtype(info: ParamInfo, stored: torch.dtype, run: torch.dtype) -> tor
 # --------------------------------------------------------------------------- cache needs
 @dataclass(frozen=True)
 class KVNeed:
-    """Keys and values of every position (window 0) or of the last `window` positions."""
+    """Keys and values of every position (window 0) or of the last `window` positions.
+
+    values=False: the mixer keeps one row per position and head only (a latent from which it
+    makes keys and values itself); the group then has no value pages."""
 
     num_kv_heads: int
     head_dim: int
     window: int = 0
     dtype: Optional[torch.dtype] = None  # None: the run's activation type
+    values: bool = True
 
 
 @dataclass(frozen=True)
@@ -159,18 +167,32 @@ class ResidualStream:
         self.x = x
         self.act_dtype = act_dtype
         self.pending: Optional[torch.Tensor] = None
+        # (weight, eps) of an RMSNorm that what is pending goes through before it is added (a layer that
+        # norms its sublayers' results); None: it is added as it is
+        self.pending_norm = None
 
-    def add(self, delta: torch.Tensor) -> None:
+    def add(self, delta: torch.Tensor, norm=None) -> None:
+        """norm: None, or (weight, eps): the stream receives rmsnorm(delta) * weight instead of delta."""
         if self.pending is not None:
             self.flush()
         self.pending = delta
+        self.pending_norm = norm
+
+    def take_pending(self):
+        """(delta, norm) of what is pending, which is the caller's to add from now on."""
+        out = (self.pending, self.pending_norm)
+        self.pending = self.pending_norm = None
+        return out
 
     def flush(self) -> None:
         from ..kernels import ops
 
         if self.pending is not None:
-            ops.add_rmsnorm(self.x, self.pending, None, 0.0, self.act_dtype)
-            self.pending = None
+            if self.pending_norm is not None:
+                ops.normed_add_rmsnorm(self.x, self.pending, self.pending_norm[0], self.pending_norm[1], None, 0.0, self.act_dtype)
+            else:
+                ops.add_rmsnorm(self.x, self.pending, None, 0.0, self.act_dtype)
+            self.pending = self.pending_norm = None
 
 
 class Norm(Part):

@@ -8,6 +8,7 @@ import torch
 
 from ..kernels import ops
 from ..kernels.linear import STREAM_MAX_ROWS, linear_to_stream
+from ..errors import ConfigError
 from .base import BLOCKS, Block, ResidualStream
 
 
@@ -70,3 +71,31 @@ class PreNormBlock(Block):
         h = ops.gemv_stream(xw, w_gate_up, torch.bfloat16, swiglu=True, row_scale=(sumsq, blocks, d, eps))
         stream.add(linear_to_stream(h, w_down))
         return True
+
+
+@BLOCKS.register("sandwich")
+class SandwichBlock(Block):
+    """x += norm_mo(mixer(norm_m(x))); x += norm_fo(feed_forward(norm_f(x))): every sublayer has a norm before it and a
+    norm of its own result.  norms: "mixer", "mixer_out", and with a feed-forward "feed_forward", "feed_forward_out".
+
+    A sublayer's result stays pending on the stream together with the norm it has to go through; the kernel of the next
+    norm (the next sublayer's, the next layer's or the model's final one) norms it, adds it and norms the sum, all in
+    32-bit and in one pass.  The result norms must be RMS norms (`Norm.rms_weight`)."""
+
+    def __init__(self, spec, runtime, mixer, feed_forward, norms):
+        super().__init__(spec, runtime, mixer, feed_forward, norms)
+        need = ["mixer", "mixer_out"] + (["feed_forward", "feed_forward_out"] if feed_forward is not None else [])
+        for name in need:
+            if name not in self.norms:
+                raise ConfigError(f"sandwich block: no norm '{name}'")
+        for name in need[1::2]:
+            if self.norms[name].rms_weight() is None:
+                raise ConfigError(f"sandwich block: norm '{name}' is not an RMS norm")
+
+    def forward(self, stream: ResidualStream, step, cache, shared_cache: bool = False) -> None:
+        xn = self.norms["mixer"].forward(stream)
+        stream.add(self.mixer.forward(xn, step, cache, shared_cache), norm=self.norms["mixer_out"].rms_weight())
+        if self.feed_forward is None:
+            return
+        xn = self.norms["feed_forward"].forward(stream)
+        stream.add(self.feed_forward.forward(xn, step), norm=self.norms["feed_forward_out"].rms_weight())

@@ -15,19 +15,21 @@ from .base import EMBEDDINGS, HEADS, ParamInfo, Part, ResidualStream
 class TokenEmbedding(Part):
     """x = E[token], a row copy without scale (src/model.rs:1237-1242), widened to the 32-bit stream.
 
-    params: vocab_size, hidden_size.  tensor: <prefix>weight [V, d]."""
+    params: vocab_size, hidden_size, name (optional: the tensor's name after the prefix, "weight" if absent).
+    tensor: <prefix>weight [V, d]."""
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         self.vocab_size = int(self._param("vocab_size"))
         self.d = int(self._param("hidden_size"))
+        self.tensor_name = self.prefix + str(spec.params.get("name", "weight"))
         self.weight: Optional[torch.Tensor] = None
 
     def param_infos(self) -> Dict[str, ParamInfo]:
-        return {self.prefix + "weight": ParamInfo((self.vocab_size, self.d))}
+        return {self.tensor_name: ParamInfo((self.vocab_size, self.d))}
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
-        self.weight = tensors[self.prefix + "weight"]
+        self.weight = tensors[self.tensor_name]
 
     def forward(self, tokens: torch.Tensor) -> ResidualStream:
         return ResidualStream(ops.embed_gather(tokens, self.weight), self.rt.dtype)
@@ -38,7 +40,7 @@ class LinearHead(Part):
     """logits = W xn in 32-bit (src/model.rs:1366); `tied_to` names the embedding
     tensor that serves as W when the model has no classifier of its own (src/model.rs:469-473).
 
-    params: vocab_size, hidden_size, tied_to (a tensor name or None)."""
+    params: vocab_size, hidden_size, tied_to (a tensor name or None), name (optional, as for the embedding)."""
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -48,7 +50,7 @@ class LinearHead(Part):
         self.weight: Optional[torch.Tensor] = None
 
     def weight_name(self) -> str:
-        return self.tied_to or (self.prefix + "weight")
+        return self.tied_to or (self.prefix + str(self.spec.params.get("name", "weight")))
 
     def param_infos(self) -> Dict[str, ParamInfo]:
         return {self.weight_name(): ParamInfo((self.vocab_size, self.d))}

@@ -17,7 +17,12 @@ class GatedMLP(FeedForward):
     """f = W_down (act(W_gate x) * (W_up x)) with act = silu: Llama's SwiGLU
     (src/model.rs:1336-1345, src/backend/cpu.rs:435-440).
 
-    params: hidden_size, intermediate_size, activation ("silu").
+    activation "clamped_swish" (params `limit`, `alpha`): f = W_down (g s(alpha g) (u + 1)) with g = min(W_gate x, limit),
+    u = clamp(W_up x, -limit, limit), s the logistic function; its gate and up halves follow each other in both precisions
+    and a kernel of its own applies the activation.
+
+    params: hidden_size, intermediate_size, activation ("silu" or "clamped_swish"),
+            names (optional: the three tensors' names after the prefix, keys gate up down).
     tensors: <prefix>gate_proj.weight [ff, d], up_proj.weight [ff, d], down_proj.weight [d, ff].
     gate and up are kept as one [2 ff, d] matrix so that one product serves both, the
     counterpart of the reference's `matmul_shared` (src/backend/mod.rs:44-56).  In bfloat16 their
@@ -29,28 +34,32 @@ class GatedMLP(FeedForward):
         super().__init__(spec, runtime)
         self.d = int(self._param("hidden_size"))
         self.ff = int(self._param("intermediate_size"))
-        if self._param("activation") != "silu":
-            raise ConfigError(f"gated_mlp: activation '{self._param('activation')}' is not built (only 'silu')")
+        self.activation = self._param("activation")
+        if self.activation not in ("silu", "clamped_swish"):
+            raise ConfigError(f"gated_mlp: activation '{self.activation}' is not built (only 'silu' and 'clamped_swish')")
+        if self.activation == "clamped_swish":
+            self.limit, self.alpha = float(self._param("limit")), float(self._param("alpha"))
+        self.names = dict({"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}, **dict(spec.params.get("names", {})))
         self.w_gate_up = None
         self.w_down = None
 
     def param_infos(self) -> Dict[str, ParamInfo]:
         p = self.prefix
         return {
-            p + "gate_proj.weight": ParamInfo((self.ff, self.d)),
-            p + "up_proj.weight": ParamInfo((self.ff, self.d)),
-            p + "down_proj.weight": ParamInfo((self.d, self.ff)),
+            p + self.names["gate"]: ParamInfo((self.ff, self.d)),
+            p + self.names["up"]: ParamInfo((self.ff, self.d)),
+            p + self.names["down"]: ParamInfo((self.d, self.ff)),
         }
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         p = self.prefix
-        gate, up = tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]
-        self.fused = self.rt.dtype == torch.bfloat16
+        gate, up = tensors[p + self.names["gate"]], tensors[p + self.names["up"]]
+        self.fused = self.rt.dtype == torch.bfloat16 and self.activation == "silu"
         if self.fused:
             self.w_gate_up = torch.stack([gate, up], dim=1).reshape(2 * self.ff, self.d).contiguous()
         else:
             self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
-        self.w_down = tensors[p + "down_proj.weight"].contiguous()
+        self.w_down = tensors[p + self.names["down"]].contiguous()
 
     def gated_weights(self):
         return (self.w_gate_up, self.w_down) if self.fused else None
@@ -58,6 +67,8 @@ class GatedMLP(FeedForward):
     def forward(self, xn: torch.Tensor, step) -> torch.Tensor:
         if self.fused:
             h = linear_swiglu(xn, self.w_gate_up)
+        elif self.activation == "clamped_swish":
+            h = ops.clamped_glu(linear(xn, self.w_gate_up), self.alpha, self.limit)
         else:
             h = ops.swiglu(linear(xn, self.w_gate_up))
         return linear_to_stream(h, self.w_down)

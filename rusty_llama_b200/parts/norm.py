@@ -14,25 +14,30 @@ from .base import NORMS, Norm, ParamInfo, ResidualStream
 class RMSNorm(Norm):
     """y = x / sqrt(mean(x^2) + eps) * weight (src/backend/cpu.rs:96-105).
 
-    params: size, eps.  tensor: <prefix>weight [size]."""
+    params: size, eps, name (optional: the tensor's name after the prefix, "weight" if absent).  tensor: <prefix>weight [size]."""
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         self.size = int(self._param("size"))
         self.eps = float(self._param("eps"))
+        self.tensor_name = self.prefix + str(spec.params.get("name", "weight"))
         self.weight: Optional[torch.Tensor] = None
 
     def param_infos(self) -> Dict[str, ParamInfo]:
-        return {self.prefix + "weight": ParamInfo((self.size,), "vector")}
+        return {self.tensor_name: ParamInfo((self.size,), "vector")}
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
-        self.weight = tensors[self.prefix + "weight"]
+        self.weight = tensors[self.tensor_name]
 
     def rms_weight(self):
         return self.weight, self.eps
 
     def forward(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
-        delta, stream.pending = stream.pending, None
+        delta, delta_norm = stream.take_pending()
+        if delta_norm is not None:
+            return ops.normed_add_rmsnorm(
+                stream.x, delta, delta_norm[0], delta_norm[1], self.weight, self.eps, stream.act_dtype, rows=rows, write_x=rows is None
+            )
         return ops.add_rmsnorm(
             stream.x, delta, self.weight, self.eps, stream.act_dtype, rows=rows, write_x=rows is None
         )

@@ -4,7 +4,8 @@ from __future__ import annotations
 
 import torch
 
-from ..config.rope_scaling import RopeScaling, inverse_frequencies
+from ..config.rope_scaling import RopeScaling, inverse_frequencies, magnitude
+from ..errors import ConfigError
 from ..kernels import ops
 from .base import POSITIONS, PositionEncoding
 
@@ -26,8 +27,13 @@ class Rotary(PositionEncoding):
             scaling = RopeScaling.from_json(scaling)
         table = inverse_frequencies(self.rotary_dim, float(self._param("theta")), scaling)
         self.inv_freq = torch.from_numpy(table).to(runtime.device)
+        # what cosines and sines are multiplied by (other than 1 only with "yarn" scaling); a mixer that rotates with
+        # kernels of its own reads it here
+        self.magnitude = magnitude(scaling)
 
     def write_qk(self, qkv, step, kv, num_heads, num_kv_heads, head_dim, write_kv):
+        if self.magnitude != 1.0:
+            raise ConfigError("rotary: the fused rotation and cache write of grouped-query attention has no magnitude factor")
         ops.rope_kv_write(
             qkv, step.tok_pos, step.tok_seq,
             kv.block_table if write_kv else None, kv.k_pages if write_kv else None, kv.v_pages if write_kv else None,
@@ -38,6 +44,8 @@ class Rotary(PositionEncoding):
         raise NotImplementedError("Rotary encodes positions inside write_qk")
 
     def decode_fusion(self):
+        if self.magnitude != 1.0:
+            return None
         if self.rotary_dim % 8:  # the fused kernel moves a pair's halves between lanes in steps of four values
             return None
         return self.inv_freq, self.rotary_dim, self.interleaved

@@ -40,6 +40,9 @@ def known_architectures():
 
 
 def architecture_name(config_json: Mapping[str, Any]) -> str:
+    single = config_json.get("architecture")
+    if isinstance(single, str) and "architectures" not in config_json:
+        return single  # folders that name their one architecture as a plain string
     names = config_json.get("architectures")
     if not isinstance(names, (list, tuple)) or len(names) != 1 or not isinstance(names[0], str):
         raise ConfigError(f"config.json must name exactly one architecture in 'architectures', got {names!r}")

@@ -33,11 +33,11 @@ class LayerSpec:
     """One layer: an arrangement (`block`) of a mixer, a feed-forward and norms.
 
     `norms` maps the names the arrangement uses ("mixer", "feed_forward" for a
-    pre-norm block) to norm parts."""
+    pre-norm block) to norm parts.  `feed_forward` None: the layer has a mixer only."""
 
     block: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]
     norms: Mapping[str, PartSpec]
 
 

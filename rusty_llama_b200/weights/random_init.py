@@ -39,6 +39,13 @@ def random_tensor(name: str, info: ParamInfo, seed: int, dtype: torch.dtype, std
             t += norm_jitter * torch.randn(info.shape, generator=gen, dtype=torch.float32, device=device)
     elif info.kind == "table":
         return torch.zeros(info.shape, dtype=torch.int32, device=device)
+    elif info.kind == "scalars":
+        # learned numbers that enter 32-bit arithmetic directly: single rows (a sink, a bias, a norm of a latent) are
+        # drawn wide enough to matter, matrices (a router) so that their products are of order one
+        spread = 0.5 if len(info.shape) == 1 else 1.0 / max(info.shape[-1], 1) ** 0.5
+        t = spread * torch.randn(info.shape, generator=gen, dtype=torch.float32, device=device)
+        if len(info.shape) == 1 and info.shape[0] > 16:
+            t += 1.0
     else:
         t = std * torch.randn(info.shape, generator=gen, dtype=torch.float32, device=device)
     return t.to(dtype)

@@ -49,7 +49,8 @@ def test_round_trip_through_json():
         ({"attention_bias": True}, "bias"),
         ({"hidden_act": "gelu"}, "SwiGLU"),
         ({"torch_dtype": "int8"}, "torch_dtype"),
-        ({"rope_scaling": {"rope_type": "yarn", "factor": 2.0}}, "unsupported rope_scaling"),
+        ({"rope_scaling": {"rope_type": "yarn", "factor": 2.0, "original_max_position_embeddings": 64}}, "unsupported rope_scaling"),
+        ({"rope_scaling": {"rope_type": "longrope", "factor": 2.0}}, "unsupported rope_scaling"),
         ({"rope_scaling": {"rope_type": "llama3"}}, "needs 'factor'"),
         ({"eos_token_id": 9999}, "outside the vocabulary"),
     ],
