@@ -1128,3 +1128,53 @@ def moe_combine(
     )
     _check(lib, rc, "moe_combine")
     return out
+
+
+def latent_attn_mma_takes(rank: int, rot: int) -> bool:
+    """Whether the tensor-core latent attention is built for these sizes (else `latent_attn` takes them)."""
+    return bool(build.load("latent_attention_mma").rl_latent_attn_mma_takes(c_int(rank), c_int(rot)))
+
+
+def latent_attn_mma_scratch_floats(n_rows: int, rank: int, n_splits: int) -> int:
+    return n_rows * n_splits * (rank + 2) if n_splits > 1 else 0
+
+
+def latent_attn_mma(
+    q_cat: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor, seq_start: torch.Tensor, seq_pos0: torch.Tensor, max_q_len: int,
+    sink: Optional[torch.Tensor], rank: int, rot: int, scale: float, window: int = 0, n_splits: int = 1,
+    scratch: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """`latent_attn` on the tensor cores, bfloat16: sequence s brings the tokens seq_start[s] .. seq_start[s+1]-1 of q_cat
+    [T, H, rank + rot] at positions seq_pos0[s], seq_pos0[s] + 1, ...; max_q_len: the most tokens one sequence brings.
+    n_splits > 1 cuts every sequence's key range into that many parts (float32 scratch of
+    `latent_attn_mma_scratch_floats` elements), added up by a second kernel."""
+    _cuda(q_cat, "latent_attn_mma q_cat", torch.bfloat16)
+    _need(q_cat.dim() == 3 and q_cat.shape[2] == rank + rot, "latent_attn_mma: q_cat must be [T, H, rank + rot]")
+    T, H = q_cat.shape[0], q_cat.shape[1]
+    _cuda(pages, "latent_attn_mma pages", torch.bfloat16)
+    _need(pages.dim() == 4 and tuple(pages.shape[1:]) == (1, PAGE_SIZE, rank + rot), f"latent_attn_mma: pages {tuple(pages.shape)}")
+    _need(q_cat.data_ptr() % 16 == 0 and pages.data_ptr() % 16 == 0, "latent_attn_mma: tensors must be 16-byte aligned")
+    _cuda(block_table, "latent_attn_mma block_table", torch.int32)
+    _cuda(seq_start, "latent_attn_mma seq_start", torch.int32)
+    _cuda(seq_pos0, "latent_attn_mma seq_pos0", torch.int32)
+    S = seq_pos0.numel()
+    _need(seq_start.numel() == S + 1 and block_table.dim() == 2 and block_table.shape[0] >= S, "latent_attn_mma: metadata sizes")
+    if sink is not None:
+        _cuda(sink, "latent_attn_mma sink", torch.float32)
+        _need(sink.numel() == H, "latent_attn_mma: one sink per head")
+    if n_splits > 1:
+        _cuda(scratch, "latent_attn_mma scratch", torch.float32)
+        need = latent_attn_mma_scratch_floats(T * H, rank, n_splits)
+        _need(scratch.numel() >= need, f"latent_attn_mma: scratch holds {scratch.numel()} floats, {need} needed")
+    if out is None:
+        out = torch.empty((T, H, rank), dtype=torch.bfloat16, device=q_cat.device)
+    _cuda(out, "latent_attn_mma out", torch.bfloat16)
+    _need(tuple(out.shape) == (T, H, rank), "latent_attn_mma: out has the wrong shape")
+    lib = build.load("latent_attention_mma")
+    rc = lib.rl_latent_attn_mma(
+        _p(q_cat), _p(pages), _p(block_table), c_int(block_table.shape[1]), _p(seq_start), _p(seq_pos0), _p(sink), _p(out),
+        _p(scratch) if n_splits > 1 else c_void_p(0), c_ll(T * H), c_int(S), c_int(max_q_len * H), c_int(H), c_int(rank), c_int(rot),
+        c_int(PAGE_SIZE), c_int(window), c_float(scale), c_int(n_splits), _stream(),
+    )
+    _check(lib, rc, "latent_attn_mma", kernels=2 if n_splits > 1 else 1)
+    return out

@@ -9,6 +9,7 @@ import torch
 from ..config.rope_scaling import magnitude
 from ..errors import ConfigError
 from ..kernels import ops
+from ..kernels.device import sm_count
 from ..kernels.linear import linear, linear_to_stream
 from ..spec import PartSpec
 from .base import MIXERS, POSITIONS, KVNeed, Mixer, ParamInfo
@@ -134,9 +135,25 @@ class LatentAttention(Mixer):
             ops.head_linear(q, self.dim + self.rot, self.w_ukT, q_cat.view(T, self.H * self.kvd), self.kvd)
         else:
             q_cat[:, :, : self.rank].zero_()
-        o_lat = ops.latent_attn(
-            q_cat, cache.k_pages, cache.block_table, step.tok_seq, step.tok_pos, self.sink, self.rank, self.rot, self.scale, self.window,
-        )
+        if xn.dtype == torch.bfloat16 and ops.latent_attn_mma_takes(self.rank, self.rot):
+            # tensor cores; a decode step cuts every sequence's keys into parts so that the GPU is filled once, none
+            # shorter than two pages (planned from the step's page-table width, which a captured graph keeps)
+            n_splits = 1
+            if step.decode_only:
+                blocks = step.n_seqs * ((self.H + 31) // 32 if self.H > 16 else 1)
+                pages = max(1, (step.plan_kv_len + ops.PAGE_SIZE - 1) // ops.PAGE_SIZE)
+                n_splits = max(1, min(sm_count(xn.device) // blocks, pages // 2, 64))
+            scratch = None
+            if n_splits > 1:
+                scratch = self.rt.workspace.get("latent_attn", ops.latent_attn_mma_scratch_floats(T * self.H, self.rank, n_splits), torch.float32)
+            o_lat = ops.latent_attn_mma(
+                q_cat, cache.k_pages, cache.block_table, step.seq_start, step.seq_pos0, step.max_q_len, self.sink, self.rank, self.rot,
+                self.scale, self.window, n_splits, scratch,
+            )
+        else:
+            o_lat = ops.latent_attn(
+                q_cat, cache.k_pages, cache.block_table, step.tok_seq, step.tok_pos, self.sink, self.rank, self.rot, self.scale, self.window,
+            )
         a = torch.empty((T, self.vd), dtype=xn.dtype, device=xn.device)
         ops.head_linear(o_lat.view(T, self.H * self.rank), self.rank, self.w_uv, a, self.vdim, gate=g, gate_head_stride=self.vdim)
         return a, self.w_o
