@@ -4,7 +4,7 @@
 //                s + bias are chosen (ties to the lower index), their weights are their s (optionally divided by
 //                their sum); one more row of W_r, if present, gives a per-token gate sigmoid(w_g . x)
 //   moe_plan     counts the (token, choice) pairs of each expert, lays them out expert after expert (`order`,
-//                with the inverse `place`), and cuts each expert's range into row tiles (`tiles`)
+//                with the inverse `place`), and cuts each expert's range into row tiles (`tiles`) of a given height
 //   moe_gemm     one kernel for all experts: a block takes one row tile (rows of ONE expert) and one column
 //                tile; rows are gathered through `order`; with ACT the block computes the gate and the up
 //                product together and writes act(gate) * up
@@ -23,35 +23,92 @@ RL_DEFINE_ERROR_TEXT()
 #define MOE_TK 16
 
 // ---------------------------------------------------------------- router
-// One block of 128 threads per token.  w: float32 [E (+1), d]; x in the activation type.
-template <typename T>
-__global__ void moe_router_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ w, const float* __restrict__ bias,
-                                  int E, int d, int top, int renorm, int has_gate, int* __restrict__ ids,
-                                  float* __restrict__ weights, float* __restrict__ gate) {
-  extern __shared__ float z[];  // E + 1 logits, then E choice scores
+// Two kernels.  Logits: a block takes 8 tokens and 16 rows of w (four per warp), so that a row of w is read once for 8
+// tokens and a token's activations once for four rows; every logit is one lane-strided sum
+// followed by the warp's fixed reduction, whatever else is in the batch.  Choice: one warp per token.
+// w: float32 [E (+1), d]; x in the activation type.
+#define ROUTER_TOKENS 8
+
+#define ROUTER_ROWS 4  // rows of w per warp: a token's activations are read once for four logits
+
+template <typename T, bool VEC>
+__global__ void moe_router_logits_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ w, int rows, int d, int n_tokens,
+                                         float* __restrict__ z) {
   pdl_trigger();
   pdl_wait();
-  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  const T* xr = x + (size_t)t * ldx;
-  const int rows = E + (has_gate ? 1 : 0);
-  for (int e = warp; e < rows; e += nwarps) {
-    const float* wr = w + (size_t)e * d;
-    float s = 0.f;
-    for (int k = lane; k < d; k += 32) s += to_f32(xr[k]) * wr[k];
-    s = warp_sum(s);
-    if (lane == 0) z[e] = s;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int e0 = (blockIdx.y * 4 + warp) * ROUTER_ROWS, t0 = blockIdx.x * ROUTER_TOKENS;
+  if (e0 >= rows) return;
+  float s[ROUTER_ROWS][ROUTER_TOKENS];
+#pragma unroll
+  for (int r = 0; r < ROUTER_ROWS; ++r)
+#pragma unroll
+    for (int i = 0; i < ROUTER_TOKENS; ++i) s[r][i] = 0.f;
+  if (VEC) {  // d a multiple of 8, rows 16-byte aligned: a lane takes 8 neighbouring k per round
+    for (int k = lane * 8; k < d; k += 256) {
+      float wv[ROUTER_ROWS][8];
+#pragma unroll
+      for (int r = 0; r < ROUTER_ROWS; ++r) {
+        const float* wr = w + (size_t)min(e0 + r, rows - 1) * d + k;
+        load4<float>(wr, wv[r]);
+        load4<float>(wr + 4, wv[r] + 4);
+      }
+#pragma unroll
+      for (int i = 0; i < ROUTER_TOKENS; ++i)
+        if (t0 + i < n_tokens) {
+          float xv[8];
+          load4<T>(x + (size_t)(t0 + i) * ldx + k, xv);
+          load4<T>(x + (size_t)(t0 + i) * ldx + k + 4, xv + 4);
+#pragma unroll
+          for (int r = 0; r < ROUTER_ROWS; ++r)
+#pragma unroll
+            for (int u = 0; u < 8; ++u) s[r][i] += xv[u] * wv[r][u];
+        }
+    }
+  } else {
+    for (int k = lane; k < d; k += 32) {
+      float wv[ROUTER_ROWS];
+#pragma unroll
+      for (int r = 0; r < ROUTER_ROWS; ++r) wv[r] = w[(size_t)min(e0 + r, rows - 1) * d + k];
+#pragma unroll
+      for (int i = 0; i < ROUTER_TOKENS; ++i)
+        if (t0 + i < n_tokens) {
+          const float xv = to_f32(x[(size_t)(t0 + i) * ldx + k]);
+#pragma unroll
+          for (int r = 0; r < ROUTER_ROWS; ++r) s[r][i] += xv * wv[r];
+        }
+    }
   }
-  __syncthreads();
-  if (warp != 0) return;
-  float* choice = z + E + 1;
+#pragma unroll
+  for (int r = 0; r < ROUTER_ROWS; ++r)
+#pragma unroll
+    for (int i = 0; i < ROUTER_TOKENS; ++i) {
+      const float v = warp_sum(s[r][i]);
+      if (lane == 0 && t0 + i < n_tokens && e0 + r < rows) z[(size_t)(t0 + i) * rows + e0 + r] = v;
+    }
+}
+
+// One warp per token (four tokens per block): softmax over the E logits, the `top` largest of score + bias.
+__global__ void moe_router_choose_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int E, int rows, int top,
+                                         int renorm, int n_tokens, int* __restrict__ ids, float* __restrict__ weights,
+                                         float* __restrict__ gate) {
+  extern __shared__ float sm[];  // per warp: E scores, E choice scores
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * 4 + warp;
+  if (t >= n_tokens) return;
+  float* z = sm + (size_t)warp * 2 * E;
+  float* choice = z + E;
+  const float* lg = logits + (size_t)t * rows;
   float mx = -INFINITY;
-  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, lg[e]);
   mx = warp_max(mx);
   float sum = 0.f;
-  for (int e = lane; e < E; e += 32) sum += expf(z[e] - mx);
+  for (int e = lane; e < E; e += 32) sum += expf(lg[e] - mx);
   sum = warp_sum(sum);
   for (int e = lane; e < E; e += 32) {
-    const float s = expf(z[e] - mx) / sum;
+    const float s = expf(lg[e] - mx) / sum;
     z[e] = s;
     choice[e] = s + (bias ? bias[e] : 0.f);
   }
@@ -84,82 +141,105 @@ __global__ void moe_router_kernel(const T* __restrict__ x, int ldx, const float*
   }
   if (renorm && lane == 0)
     for (int j = 0; j < top; ++j) weights[(size_t)t * top + j] /= chosen_sum;
-  if (has_gate && lane == 0) gate[t] = 1.0f / (1.0f + expf(-z[E]));
+  if (rows > E && lane == 0) gate[t] = 1.0f / (1.0f + expf(-lg[E]));
 }
 
+// logits: float32 scratch of n_tokens * (E + has_gate) values.
 RL_API int rl_moe_router(const void* x, int ldx, int dtype, const float* w, const float* bias, int n_tokens, int E, int d,
-                         int top, int renorm, int has_gate, int* ids, float* weights, float* gate, cudaStream_t stream) {
+                         int top, int renorm, int has_gate, float* logits, int* ids, float* weights, float* gate, cudaStream_t stream) {
   if (n_tokens <= 0 || E <= 0 || d <= 0 || top <= 0 || top > E) RL_REFUSE(1, "moe_router: T=%d E=%d d=%d top=%d", n_tokens, E, d, top);
   if (has_gate && gate == nullptr) RL_REFUSE(2, "moe_router: a gate row but nowhere to write the gate");
-  const size_t smem = (size_t)(2 * E + 2) * sizeof(float);
+  const size_t smem = (size_t)4 * 2 * E * sizeof(float);
   if (smem > 48 * 1024) RL_REFUSE(3, "moe_router: %d experts exceed the kernel's shared memory", E);
-  if (dtype == RL_BF16)
-    RL_LAUNCH_CHECK(rl_launch<false>(moe_router_kernel<bf16>, n_tokens, 128, smem, stream, (const bf16*)x, ldx, w, bias, E, d, top,
-                                     renorm, has_gate, ids, weights, gate));
+  const int rows = E + (has_gate ? 1 : 0);
+  dim3 grid((n_tokens + ROUTER_TOKENS - 1) / ROUTER_TOKENS, (rows + 4 * ROUTER_ROWS - 1) / (4 * ROUTER_ROWS));
+  if (grid.y > 65535) RL_REFUSE(5, "moe_router: %d experts exceed the grid", E);
+  // (which of the two loops runs depends on sizes and addresses only, never on the batch: a token's logits keep their bits)
+  const bool vec = d % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0);
+  if (dtype == RL_BF16 && vec)
+    RL_LAUNCH_CHECK(rl_launch<false>(moe_router_logits_kernel<bf16, true>, grid, 128, 0, stream, (const bf16*)x, ldx, w, rows, d, n_tokens, logits));
+  else if (dtype == RL_BF16)
+    RL_LAUNCH_CHECK(rl_launch<false>(moe_router_logits_kernel<bf16, false>, grid, 128, 0, stream, (const bf16*)x, ldx, w, rows, d, n_tokens, logits));
+  else if (dtype == RL_F32 && vec)
+    RL_LAUNCH_CHECK(rl_launch<false>(moe_router_logits_kernel<float, true>, grid, 128, 0, stream, (const float*)x, ldx, w, rows, d, n_tokens, logits));
   else if (dtype == RL_F32)
-    RL_LAUNCH_CHECK(rl_launch<false>(moe_router_kernel<float>, n_tokens, 128, smem, stream, (const float*)x, ldx, w, bias, E, d,
-                                     top, renorm, has_gate, ids, weights, gate));
+    RL_LAUNCH_CHECK(rl_launch<false>(moe_router_logits_kernel<float, false>, grid, 128, 0, stream, (const float*)x, ldx, w, rows, d, n_tokens, logits));
   else
     RL_REFUSE(4, "moe_router: unknown dtype %d", dtype);
+  RL_LAUNCH_CHECK(rl_launch<false>(moe_router_choose_kernel, (n_tokens + 3) / 4, 128, smem, stream, (const float*)logits, bias, E, rows, top,
+                                   renorm, n_tokens, ids, weights, gate));
   return 0;
 }
 
 // ---------------------------------------------------------------- plan
 // ids[n] (n = T * top pairs) -> order[n] (pairs laid out expert after expert, each expert's pairs in ascending
 // pair index), place[pair] (its row in that layout), tiles[1 + 3 * max_tiles]: the number of tiles, then
-// (expert, first row, rows) per tile.  One block; E counters in shared memory.
-__global__ void moe_plan_kernel(const int* __restrict__ ids, int n, int E, int* __restrict__ order, int* __restrict__ place,
-                                int* __restrict__ tiles) {
-  extern __shared__ int cnt[];  // E counts, then E + 1 offsets
+// (expert, first row, rows) per tile.  One block per expert: every block counts all experts' pairs in shared memory
+// (it needs the counts of the experts before its own for its first row and its first tile), then lays out its own
+// expert's pairs, each thread a contiguous piece of the pairs so that their order is kept.
+#define PLAN_THREADS 512
+
+__global__ void __launch_bounds__(PLAN_THREADS)
+moe_plan_kernel(const int* __restrict__ ids, int n, int E, int* __restrict__ order, int* __restrict__ place,
+                int* __restrict__ tiles, int tile_rows) {
+  extern __shared__ int cnt[];  // E counts
+  __shared__ int scan[PLAN_THREADS];
+  __shared__ int first_row, first_tile;
   pdl_trigger();
   pdl_wait();
-  int* off = cnt + E;
-  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+  const int e = blockIdx.x, tid = threadIdx.x;
+  for (int i = tid; i < E; i += PLAN_THREADS) cnt[i] = 0;
   __syncthreads();
-  for (int i = threadIdx.x; i < n; i += blockDim.x) atomicAdd(&cnt[ids[i]], 1);
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int at = 0, nt = 0;
-    for (int e = 0; e < E; ++e) {
-      off[e] = at;
-      for (int r = 0; r < cnt[e]; r += MOE_TM) {
-        tiles[1 + 3 * nt] = e;
-        tiles[2 + 3 * nt] = at + r;
-        tiles[3 + 3 * nt] = min(MOE_TM, cnt[e] - r);
-        ++nt;
-      }
-      at += cnt[e];
-    }
-    off[E] = at;
-    tiles[0] = nt;
+  const int per = (n + PLAN_THREADS - 1) / PLAN_THREADS;
+  const int lo = min(n, tid * per), hi = min(n, lo + per);
+  int mine = 0;
+  for (int i = lo; i < hi; ++i) {
+    const int id = ids[i];
+    atomicAdd(&cnt[id], 1);
+    mine += id == e;
   }
+  scan[tid] = mine;
   __syncthreads();
-  // a pair's row: its expert's offset plus the number of earlier pairs of the same expert.  One warp per
-  // expert walks the pairs in order, so the layout is the same on every run.
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  for (int e = warp; e < E; e += nwarps) {
-    int at = off[e];
-    for (int base = 0; base < n; base += 32) {
-      const int i = base + lane;
-      const bool mine = i < n && ids[i] == e;
-      const unsigned m = __ballot_sync(0xffffffffu, mine);
-      if (mine) {
-        const int r = at + __popc(m & ((1u << lane) - 1u));
-        order[r] = i;
-        place[i] = r;
-      }
-      at += __popc(m);
+  if (tid == 0) {
+    int at = 0, nt = 0;
+    for (int k = 0; k < e; ++k) {
+      at += cnt[k];
+      nt += (cnt[k] + tile_rows - 1) / tile_rows;
     }
+    first_row = at;
+    first_tile = nt;
+    if (e == E - 1) tiles[0] = nt + (cnt[e] + tile_rows - 1) / tile_rows;
+  }
+  // exclusive scan of the threads' counts (Hillis-Steele over the block)
+  for (int o = 1; o < PLAN_THREADS; o <<= 1) {
+    const int v = tid >= o ? scan[tid - o] : 0;
+    __syncthreads();
+    scan[tid] += v;
+    __syncthreads();
+  }
+  int r = first_row + scan[tid] - mine;
+  for (int i = lo; i < hi; ++i)
+    if (ids[i] == e) {
+      order[r] = i;
+      place[i] = r;
+      ++r;
+    }
+  const int c = cnt[e];
+  for (int k = tid; k * tile_rows < c; k += PLAN_THREADS) {
+    int* t = tiles + 1 + 3 * (first_tile + k);
+    t[0] = e;
+    t[1] = first_row + k * tile_rows;
+    t[2] = min(tile_rows, c - k * tile_rows);
   }
 }
 
 RL_API int rl_moe_tile_rows() { return MOE_TM; }
 
-RL_API int rl_moe_plan(const int* ids, int n, int E, int* order, int* place, int* tiles, cudaStream_t stream) {
-  if (n <= 0 || E <= 0) RL_REFUSE(1, "moe_plan: n=%d E=%d", n, E);
-  const size_t smem = (size_t)(2 * E + 1) * sizeof(int);
-  if (smem > 48 * 1024) RL_REFUSE(2, "moe_plan: %d experts exceed the kernel's shared memory", E);
-  RL_LAUNCH_CHECK(rl_launch<false>(moe_plan_kernel, 1, 1024, smem, stream, ids, n, E, order, place, tiles));
+RL_API int rl_moe_plan(const int* ids, int n, int E, int* order, int* place, int* tiles, int tile_rows, cudaStream_t stream) {
+  if (n <= 0 || E <= 0 || tile_rows <= 0) RL_REFUSE(1, "moe_plan: n=%d E=%d tile_rows=%d", n, E, tile_rows);
+  const size_t smem = (size_t)E * sizeof(int);
+  if (smem > 40 * 1024) RL_REFUSE(2, "moe_plan: %d experts exceed the kernel's shared memory", E);
+  RL_LAUNCH_CHECK(rl_launch<false>(moe_plan_kernel, E, PLAN_THREADS, smem, stream, ids, n, E, order, place, tiles, tile_rows));
   return 0;
 }
 
@@ -243,6 +323,7 @@ moe_gemm_kernel(const TA* __restrict__ x, int ldx, const int* __restrict__ order
   }
 }
 
+// (the plan's tiles must be MOE_TM rows high: `rl_moe_tile_rows`)
 RL_API int rl_moe_gemm(const void* x, int ldx, int dtype, const int* order, int gather_div, const void* w, const void* w2,
                        void* out, int out_dtype, int ldo, const int* tiles, int max_tiles, int N, int K, cudaStream_t stream) {
   if (max_tiles <= 0 || N <= 0 || K <= 0 || gather_div <= 0) RL_REFUSE(1, "moe_gemm: tiles=%d N=%d K=%d div=%d", max_tiles, N, K, gather_div);

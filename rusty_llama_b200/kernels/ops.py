@@ -986,6 +986,14 @@ def head_linear(
         _cuda(gate, "head_linear gate", x.dtype, contiguous=False)
         ldg = _rows(gate, "head_linear gate")
         _need(gate.shape[0] == M and (H - 1) * gate_head_stride + N <= gate.shape[1], "head_linear: gate rows do not fit")
+    if x.dtype == torch.bfloat16 and grouped_gemm_takes(K, ldx, x_head_stride) and x.data_ptr() % 16 == 0:
+        lib = build.load("grouped_gemm")
+        rc = lib.rl_head_linear_mma(
+            _p(x), c_int(ldx), c_int(x_head_stride), _p(w), _p(out), c_int(ldo), c_int(out_head_stride), _p(gate), c_int(ldg),
+            c_int(gate_head_stride), c_int(M), c_int(H), c_int(N), c_int(K), _stream(),
+        )
+        _check(lib, rc, "head_linear_mma")
+        return out
     lib = build.load("latent_attention")
     rc = lib.rl_head_linear(
         _p(x), c_int(ldx), c_int(x_head_stride), _p(w), c_ll(N * K), c_int(K), c_int(1), _p(out), c_int(ldo), c_int(out_head_stride),
@@ -1028,6 +1036,11 @@ def latent_attn(
 
 
 # ------------------------------------------------------------------ routed feed-forward
+def grouped_gemm_takes(K: int, ldx: int, head_stride: int) -> bool:
+    """Whether the tensor-core products of `grouped_gemm.cu` take operands with this k and these strides (in elements)."""
+    return bool(build.load("grouped_gemm").rl_grouped_gemm_takes(c_int(K), c_int(ldx), c_int(head_stride)))
+
+
 def moe_tile_rows() -> int:
     return int(build.load("moe").rl_moe_tile_rows())
 
@@ -1048,42 +1061,50 @@ def moe_router(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], n
     ids = torch.empty((T, top), dtype=torch.int32, device=x.device)
     weights = torch.empty((T, top), dtype=torch.float32, device=x.device)
     gate = torch.empty((T,), dtype=torch.float32, device=x.device) if has_gate else None
+    logits = torch.empty((T, w.shape[0]), dtype=torch.float32, device=x.device)
     lib = build.load("moe")
     rc = lib.rl_moe_router(
         _p(x), c_int(_rows(x, "moe_router x")), c_int(_dt(x, "moe_router")), _p(w), _p(bias), c_int(T), c_int(n_experts), c_int(d), c_int(top),
-        c_int(1 if renormalize else 0), c_int(1 if has_gate else 0), _p(ids), _p(weights), _p(gate), _stream(),
+        c_int(1 if renormalize else 0), c_int(1 if has_gate else 0), _p(logits), _p(ids), _p(weights), _p(gate), _stream(),
     )
-    _check(lib, rc, "moe_router")
+    _check(lib, rc, "moe_router", kernels=2)
     return ids, weights, gate
 
 
-def moe_max_tiles(n_pairs: int, n_experts: int) -> int:
+MOE_MMA_TILE_ROWS = (32, 128)  # tile heights the tensor-core products are built for
+
+
+def moe_max_tiles(n_pairs: int, n_experts: int, tile_rows: int = 0) -> int:
     """Upper bound of the row tiles that `moe_plan` makes of n_pairs (token, choice) pairs."""
-    rows = moe_tile_rows()
+    rows = tile_rows or moe_tile_rows()
     return min(n_pairs, n_pairs // rows + n_experts)
 
 
-def moe_plan(ids: torch.Tensor, n_experts: int):
-    """ids int32 [T, top] -> (order [T top], place [T top], tiles [1 + 3 max_tiles], max_tiles), all on the device."""
+def moe_plan(ids: torch.Tensor, n_experts: int, tile_rows: int = 0):
+    """ids int32 [T, top] -> (order [T top], place [T top], tiles [1 + 3 max_tiles], max_tiles), all on the device.
+    tile_rows: the height of a row tile (0: the plain product's)."""
     _cuda(ids, "moe_plan ids", torch.int32)
     n = ids.numel()
-    max_tiles = moe_max_tiles(n, n_experts)
+    tile_rows = tile_rows or moe_tile_rows()
+    max_tiles = moe_max_tiles(n, n_experts, tile_rows)
     order = torch.empty((n,), dtype=torch.int32, device=ids.device)
     place = torch.empty((n,), dtype=torch.int32, device=ids.device)
     tiles = torch.empty((1 + 3 * max_tiles,), dtype=torch.int32, device=ids.device)
     lib = build.load("moe")
-    rc = lib.rl_moe_plan(_p(ids), c_int(n), c_int(n_experts), _p(order), _p(place), _p(tiles), _stream())
+    rc = lib.rl_moe_plan(_p(ids), c_int(n), c_int(n_experts), _p(order), _p(place), _p(tiles), c_int(tile_rows), _stream())
     _check(lib, rc, "moe_plan")
     return order, place, tiles, max_tiles
 
 
 def moe_gemm(
     x: torch.Tensor, w: torch.Tensor, tiles: torch.Tensor, max_tiles: int, n_rows: int, order: Optional[torch.Tensor] = None,
-    gather_div: int = 1, w2: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+    gather_div: int = 1, w2: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None, tile_rows: int = 0,
 ) -> torch.Tensor:
     """out[r] = w[expert of r] . x[row of r] for the n_rows rows of a plan's layout; w: [E, N, K].
 
-    order given: row r reads x[order[r] // gather_div], else x[r].  w2 given: out = silu(w x) * (w2 x)."""
+    order given: row r reads x[order[r] // gather_div], else x[r].  w2 given: out = silu(w x) * (w2 x).
+    tile_rows: the height of the plan's tiles; bfloat16 operands whose rows can be moved in 16-byte pieces go to the
+    tensor cores if it is one of MOE_MMA_TILE_ROWS, everything else to the plain kernel (which wants its own height)."""
     _cuda(x, "moe_gemm x", contiguous=False)
     _cuda(w, "moe_gemm w", x.dtype)
     _need(w.dim() == 3 and w.shape[2] == x.shape[1], f"moe_gemm: w {tuple(w.shape)} against x {tuple(x.shape)}")
@@ -1093,6 +1114,16 @@ def moe_gemm(
         _need(tuple(w2.shape) == (E, N, K), "moe_gemm: w2 does not match w")
     out_dtype = out_dtype or x.dtype
     out = torch.empty((n_rows, N), dtype=out_dtype, device=x.device)
+    tile_rows = tile_rows or moe_tile_rows()
+    if x.dtype == torch.bfloat16 and tile_rows in MOE_MMA_TILE_ROWS and grouped_gemm_takes(K, x.stride(0), 0) and x.data_ptr() % 16 == 0:
+        lib = build.load("grouped_gemm")
+        rc = lib.rl_moe_gemm_mma(
+            _p(x), c_int(x.stride(0)), _p(order), c_int(gather_div), _p(w), _p(w2), _p(out), c_int(_dt(out, "moe_gemm out")), c_int(N),
+            _p(tiles), c_int(max_tiles), c_int(tile_rows), c_int(N), c_int(K), _stream(),
+        )
+        _check(lib, rc, "moe_gemm_mma")
+        return out
+    _need(tile_rows == moe_tile_rows(), f"moe_gemm: the plain kernel wants tiles of {moe_tile_rows()} rows, the plan has {tile_rows}")
     lib = build.load("moe")
     rc = lib.rl_moe_gemm(
         _p(x), c_int(_rows(x, "moe_gemm x")), c_int(_dt(x, "moe_gemm")), _p(order), c_int(gather_div), _p(w), _p(w2), _p(out),

@@ -90,9 +90,14 @@ class RoutedExperts(FeedForward):
     def forward(self, xn: torch.Tensor, step) -> torch.Tensor:
         T = xn.shape[0]
         ids, weights, gate = ops.moe_router(xn, self.w_router, self.bias, self.E, self.top, self.renormalize)
-        order, place, tiles, max_tiles = ops.moe_plan(ids, self.E)
-        h = ops.moe_gemm(xn, self.w_gate, tiles, max_tiles, T * self.top, order=order, gather_div=self.top, w2=self.w_up)
-        y = ops.moe_gemm(h, self.w_down, tiles, max_tiles, T * self.top, out_dtype=torch.float32)
+        # the height of a row tile: 128 once the experts get that many rows on average (a prompt step), else 32; the plain
+        # kernels of a 32-bit run have their own
+        tile_rows = 0
+        if xn.dtype == torch.bfloat16 and self.d % 8 == 0 and self.ff % 8 == 0:  # (else the plain products, 16-byte rows or not)
+            tile_rows = 128 if T * self.top >= 64 * self.E else 32
+        order, place, tiles, max_tiles = ops.moe_plan(ids, self.E, tile_rows)
+        h = ops.moe_gemm(xn, self.w_gate, tiles, max_tiles, T * self.top, order=order, gather_div=self.top, w2=self.w_up, tile_rows=tile_rows)
+        y = ops.moe_gemm(h, self.w_down, tiles, max_tiles, T * self.top, out_dtype=torch.float32, tile_rows=tile_rows)
         shared = None
         if self.shared_ff:
             hs = linear_swiglu(xn, self.ws_gate_up) if self.shared_fused else ops.swiglu(linear(xn, self.ws_gate_up))
