@@ -97,6 +97,26 @@ __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
 
+// What a gated feed-forward makes of its two 32-bit sums g (gate) and u (up).  limit <= 0: silu(g) * u.
+// limit > 0: g' * logistic(alpha * g') * (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit).
+__device__ __forceinline__ float gated_act(float g, float u, float alpha, float limit) {
+  if (limit > 0.f) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit) + 1.0f;
+    return g * (1.0f / (1.0f + expf(-alpha * g))) * u;
+  }
+  return g * (1.0f / (1.0f + expf(-g))) * u;
+}
+// the same with the hardware's approximations of exp and of the division (a few units in the last place of 32 bits)
+__device__ __forceinline__ float gated_act_fast(float g, float u, float alpha, float limit) {
+  if (limit > 0.f) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit) + 1.0f;
+    return __fdividef(g, 1.0f + __expf(-alpha * g)) * u;
+  }
+  return __fdividef(g, 1.0f + __expf(-g)) * u;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -434,7 +434,7 @@ RL_API int rl_clamped_glu(const void* gate_up, void* h, int act_dtype, int n_tok
 //   v = x[t] + s / sqrt(mean(s^2) + eps_d) * wd                 x[t] = v
 //   if w: out[t] = v / sqrt(mean(v^2) + eps) * w
 // One block per row, the row in shared memory between the passes; every sum in the block's fixed order.
-template <typename TA, typename TW, typename TD>
+template <typename TA, typename TW, typename TD, bool VEC>
 __global__ void normed_add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_parts, long long part_stride,
                                           const TW* __restrict__ wd, float eps_d, const TW* __restrict__ w, float eps,
                                           TA* __restrict__ out, const int* __restrict__ rows, int d, int write_x) {
@@ -445,25 +445,67 @@ __global__ void normed_add_rmsnorm_kernel(float* __restrict__ x, const TD* __res
   const int r = blockIdx.x;
   const int t = rows ? rows[r] : r;
   float* xr = x + (size_t)t * d;
+  TA* o = out + (size_t)r * d;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) {
-    float s = 0.f;
-    for (int p = 0; p < n_parts; ++p) s += to_f32(delta[(size_t)p * part_stride + (size_t)t * d + i]);
-    row[i] = s;
-    ss += s * s;
+  if (VEC) {  // d a multiple of 4: four neighbouring values a thread and round, the same sums in the same order
+    for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
+      float s[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int p = 0; p < n_parts; ++p) {
+        float dv[4];
+        load4_g<TD>(delta + (size_t)p * part_stride + (size_t)t * d + i, dv);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[e] += dv[e];
+      }
+      store4<float>(row + i, s);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) ss += s[e] * s[e];
+    }
+  } else {
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+      float s = 0.f;
+      for (int p = 0; p < n_parts; ++p) s += to_f32(delta[(size_t)p * part_stride + (size_t)t * d + i]);
+      row[i] = s;
+      ss += s * s;
+    }
   }
   const float inv_d = 1.0f / sqrtf(block_sum(ss, red) / (float)d + eps_d);
   ss = 0.f;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) {
-    const float v = xr[i] + row[i] * inv_d * to_f32(wd[i]);
-    row[i] = v;
-    if (write_x) xr[i] = v;
-    ss += v * v;
+  if (VEC) {
+    for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
+      float v[4], s[4], wv[4];
+      load4_g<float>(xr + i, v);
+      load4<float>(row + i, s);
+      load4_g<TW>(wd + i, wv);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        v[e] += s[e] * inv_d * wv[e];
+        ss += v[e] * v[e];
+      }
+      store4<float>(row + i, v);
+      if (write_x) store4<float>(xr + i, v);
+    }
+  } else {
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+      const float v = xr[i] + row[i] * inv_d * to_f32(wd[i]);
+      row[i] = v;
+      if (write_x) xr[i] = v;
+      ss += v * v;
+    }
   }
   if (w == nullptr) return;
   const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)d + eps);
-  TA* o = out + (size_t)r * d;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_f32<TA>(row[i] * inv * to_f32(w[i]));
+  if (VEC) {
+    for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
+      float v[4], wv[4];
+      load4<float>(row + i, v);
+      load4_g<TW>(w + i, wv);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[e] = v[e] * inv * wv[e];
+      store4<TA>(o + i, v);
+    }
+  } else {
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_f32<TA>(row[i] * inv * to_f32(w[i]));
+  }
 }
 
 RL_API int rl_normed_add_rmsnorm(float* x, const void* delta, int delta_dtype, int n_parts, long long part_stride, const void* wd,
@@ -474,12 +516,19 @@ RL_API int rl_normed_add_rmsnorm(float* x, const void* delta, int delta_dtype, i
   if (w != nullptr && out == nullptr) RL_REFUSE(2, "normed_add_rmsnorm: a weight but no output");
   const size_t smem = (size_t)d * sizeof(float);
   if (smem > 48 * 1024) RL_REFUSE(3, "normed_add_rmsnorm: a row of %d values does not fit shared memory", d);
-  int th = ((d + 31) / 32) * 32;
-  th = th > 512 ? 512 : th;
+  // (which body runs and with how many threads depends on d and on addresses only: a row's bits do not depend on the step)
+  const bool vec = d % 4 == 0 && (((uintptr_t)x | (uintptr_t)delta | (uintptr_t)wd | (uintptr_t)w | (uintptr_t)out) % 16 == 0) &&
+                   (part_stride % 4 == 0);
+  const int th = vec ? row_threads(d) : (d >= 512 ? 512 : ((d + 31) / 32) * 32);
 #define RL_NN(TA, TW, TD)                                                                                                       \
   do {                                                                                                                          \
-    RL_LAUNCH_CHECK(rl_launch<false>(normed_add_rmsnorm_kernel<TA, TW, TD>, n_rows, th, smem, stream, x, (const TD*)delta, n_parts, \
-                                     part_stride, (const TW*)wd, eps_d, (const TW*)w, eps, (TA*)out, rows, d, write_x));        \
+    if (vec)                                                                                                                    \
+      RL_LAUNCH_CHECK(rl_launch(normed_add_rmsnorm_kernel<TA, TW, TD, true>, n_rows, th, smem, stream, x, (const TD*)delta,    \
+                                n_parts, part_stride, (const TW*)wd, eps_d, (const TW*)w, eps, (TA*)out, rows, d, write_x));    \
+    else                                                                                                                        \
+      RL_LAUNCH_CHECK(rl_launch<false>(normed_add_rmsnorm_kernel<TA, TW, TD, false>, n_rows, th, smem, stream, x,               \
+                                       (const TD*)delta, n_parts, part_stride, (const TW*)wd, eps_d, (const TW*)w, eps,          \
+                                       (TA*)out, rows, d, write_x));                                                            \
     return 0;                                                                                                                   \
   } while (0)
   if (act_dtype == RL_BF16 && w_dtype == RL_BF16 && delta_dtype == RL_BF16) RL_NN(bf16, bf16, bf16);

@@ -20,11 +20,12 @@ RL_DEFINE_ERROR_TEXT()
 #define TN 64
 #define TK 16
 
-// SWIGLU: w's rows alternate gate and up; out[M, N/2] = silu(gate) * up from the 32-bit sums.
+// SWIGLU: w's rows alternate gate and up; out[M, N/2] = gated_act(gate, up) from the 32-bit sums (silu(gate) * up,
+// or the form with limits: see common.cuh).
 template <typename TA, typename TO, bool SWIGLU>
 __global__ void __launch_bounds__(256)
 gemm_fma_kernel(const TA* __restrict__ x, int ldx, const TA* __restrict__ w, int ldw,
-                TO* __restrict__ out, int ldo, int M, int N, int K) {
+                TO* __restrict__ out, int ldo, int M, int N, int K, float act_alpha, float act_limit) {
   __shared__ float xs[TK][TM + 4];
   __shared__ float ws[TK][TN + 4];
   const int tid = threadIdx.x;
@@ -69,7 +70,7 @@ gemm_fma_kernel(const TA* __restrict__ x, int ldx, const TA* __restrict__ w, int
 #pragma unroll
       for (int j = 0; j < 4; j += 2) {
         const int n = n0 + tx * 4 + j;  // even: the gate's row; n + 1: the up's
-        if (n + 1 < N) out[(size_t)m * ldo + n / 2] = from_f32<TO>(acc[i][j] * (1.0f / (1.0f + expf(-acc[i][j]))) * acc[i][j + 1]);
+        if (n + 1 < N) out[(size_t)m * ldo + n / 2] = from_f32<TO>(gated_act(acc[i][j], acc[i][j + 1], act_alpha, act_limit));
       }
     } else {
 #pragma unroll
@@ -88,20 +89,20 @@ RL_API int rl_gemm_f32(const float* x, int ldx, const float* w, int ldw, float* 
   const int gy = (M + TM - 1) / TM;
   if (gy > 65535) RL_REFUSE(3, "gemm_f32: %d rows exceed %d", M, 65535 * TM);
   dim3 grid((N + TN - 1) / TN, gy);
-  gemm_fma_kernel<float, float, false><<<grid, 256, 0, stream>>>(x, ldx, w, ldw, out, ldo, M, N, K);
+  gemm_fma_kernel<float, float, false><<<grid, 256, 0, stream>>>(x, ldx, w, ldw, out, ldo, M, N, K, 1.f, 0.f);
   RL_LAUNCH_RESULT();
 }
 
 // bfloat16 operands of any k and any alignment; out_dtype bfloat16 or float32.
 RL_API int rl_gemm_bf16_any(const bf16* x, int ldx, const bf16* w, int ldw, void* out, int out_dtype, int ldo, int M,
-                            int N, int K, int swiglu, cudaStream_t stream) {
+                            int N, int K, int swiglu, float act_alpha, float act_limit, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) RL_REFUSE(1, "gemm_bf16_any: M=%d N=%d K=%d", M, N, K);
   if (swiglu && (N & 1)) RL_REFUSE(4, "gemm_bf16_any: %d rows of gate and up are not pairs", N);
   if (ldx < K || ldw < K || ldo < (swiglu ? N / 2 : N)) RL_REFUSE(2, "gemm_bf16_any: leading sizes %d/%d/%d too small", ldx, ldw, ldo);
   const int gy = (M + TM - 1) / TM;
   if (gy > 65535) RL_REFUSE(3, "gemm_bf16_any: %d rows exceed %d", M, 65535 * TM);
   dim3 grid((N + TN - 1) / TN, gy);
-#define RL_ANY(TO, SW) gemm_fma_kernel<bf16, TO, SW><<<grid, 256, 0, stream>>>(x, ldx, w, ldw, (TO*)out, ldo, M, N, K)
+#define RL_ANY(TO, SW) gemm_fma_kernel<bf16, TO, SW><<<grid, 256, 0, stream>>>(x, ldx, w, ldw, (TO*)out, ldo, M, N, K, act_alpha, act_limit)
   if (out_dtype == RL_BF16 && swiglu) RL_ANY(bf16, true);
   else if (out_dtype == RL_BF16) RL_ANY(bf16, false);
   else if (out_dtype == RL_F32 && swiglu) RL_ANY(float, true);

@@ -85,7 +85,7 @@ __device__ __forceinline__ void store_row32<float>(float* dst, const uint32_t (&
 
 // 32 accumulator columns that alternate gate and up -> 16 values silu(gate) * up
 template <typename TO>
-__device__ __forceinline__ void store_swiglu16(TO* dst, const uint32_t (&r)[32], int n_valid, bool vec) {
+__device__ __forceinline__ void store_swiglu16(TO* dst, const uint32_t (&r)[32], int n_valid, bool vec, float act_alpha, float act_limit) {
   float h[16];
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
@@ -93,7 +93,7 @@ __device__ __forceinline__ void store_swiglu16(TO* dst, const uint32_t (&r)[32],
     // exp and the division by the hardware's approximations (a few units in the last place of 32 bits,
     // far below the bfloat16 rounding that follows): the accurate forms cost a row's thread about 8 us per
     // tile, which a step with one tile per SM cannot hide behind the next tile's products
-    h[i] = __fdividef(g, 1.0f + __expf(-g)) * u;
+    h[i] = gated_act_fast(g, u, act_alpha, act_limit);
   }
   if (vec && n_valid >= 16) {
 #pragma unroll
@@ -131,7 +131,7 @@ __device__ __forceinline__ void store_rows32_f32(float* out_tile, int ldo, int r
 }
 // the same after SwiGLU: 64 accumulator columns (gate and up alternating) -> 32 outputs = 64 bytes a row
 __device__ __forceinline__ void store_rows32_swiglu_bf16(bf16* out_tile, int ldo, int rows_valid, const uint32_t (&r0)[32], const uint32_t (&r1)[32],
-                                                         uint32_t stage, int lane) {
+                                                         uint32_t stage, int lane, float act_alpha, float act_limit) {
 #pragma unroll
   for (int p = 0; p < 4; ++p) {
     const uint32_t* r = p < 2 ? r0 : r1;
@@ -140,7 +140,7 @@ __device__ __forceinline__ void store_rows32_swiglu_bf16(bf16* out_tile, int ldo
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const float g = __uint_as_float(r[b + 2 * i]), u = __uint_as_float(r[b + 2 * i + 1]);
-      h[i] = __fdividef(g, 1.0f + __expf(-g)) * u;  // (as in store_swiglu16)
+      h[i] = gated_act_fast(g, u, act_alpha, act_limit);  // (as in store_swiglu16)
     }
     asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(stage + lane * 64 + ((p ^ ((lane >> 1) & 3)) << 4)), "r"(pack2(h[0], h[1])),
                  "r"(pack2(h[2], h[3])), "r"(pack2(h[4], h[5])), "r"(pack2(h[6], h[7]))
@@ -170,7 +170,7 @@ template <typename TO, bool SWIGLU, bool SMALL_A>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                TO* __restrict__ out, int ldo, int M, int N, int K, int vec_store, int k_splits, int bn,
-               int* __restrict__ status, int test_role, uint32_t test_ns) {
+               int* __restrict__ status, int test_role, uint32_t test_ns, float act_alpha, float act_limit) {
   extern __shared__ unsigned char smem_dyn[];
   // the swizzled stages must start on a 1024-byte boundary
   unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
@@ -371,7 +371,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           const int col = n0 + c * 32;
           bf16* tile_out = reinterpret_cast<bf16*>(out_k) + (size_t)(m0 + quarter * 32) * ldo + (SWIGLU ? (col >> 1) : col);
           if (SWIGLU)
-            store_rows32_swiglu_bf16(tile_out, ldo, rows_valid, r0, r1, out_stage, lane);
+            store_rows32_swiglu_bf16(tile_out, ldo, rows_valid, r0, r1, out_stage, lane, act_alpha, act_limit);
           else
             store_rows64_bf16(tile_out, ldo, rows_valid, r0, r1, out_stage, lane);
         }
@@ -389,7 +389,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
         if (row < M && n_valid > 0) {
           if (SWIGLU)
-            store_swiglu16<TO>(out_k + (size_t)row * ldo + (col >> 1), r, n_valid >> 1, vec_store != 0);
+            store_swiglu16<TO>(out_k + (size_t)row * ldo + (col >> 1), r, n_valid >> 1, vec_store != 0, act_alpha, act_limit);
           else
             store_row32<TO>(out_k + (size_t)row * ldo + col, r, n_valid, vec_store != 0);
         }
@@ -417,15 +417,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 // status: one int in device memory, 0 before the call; non-zero afterwards means a bounded wait expired
 // (1 producer, 2 tensor-core issuer waiting for data, 3 epilogue, 4 tensor-core issuer waiting for the
 // epilogue) and the output is not valid.
-// swiglu != 0: w holds N rows alternating gate and up, out gets N / 2 columns (see the kernel).
+// swiglu != 0: w holds N rows alternating gate and up, out gets N / 2 columns (see the kernel); act_alpha, act_limit:
+// which activation (gated_act of common.cuh; limit <= 0 is silu(gate) * up).
 // k_splits > 1: the k range is cut into that many slices (rounded so that none is empty; the number
 // used is returned through *k_splits_used), out is [slices][M][ldo] float32 partial results.
 // wait_test_role, wait_test_ns: 0, 0 in normal use.  A test names one of the codes above and a limit in
 // nanoseconds: the waits of that role then give up after that long instead of a second.
 // tile_n: 0, or the tile width the caller wants (a multiple of 16 up to 256) in the place of the launcher's choice.
 RL_API int rl_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* out, int out_dtype, int ldo, int M, int N,
-                      int K, int swiglu, int k_splits, int* k_splits_used, int tile_n, int* status, int wait_test_role,
-                      unsigned int wait_test_ns, cudaStream_t stream) {
+                      int K, int swiglu, float act_alpha, float act_limit, int k_splits, int* k_splits_used, int tile_n, int* status,
+                      int wait_test_role, unsigned int wait_test_ns, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) RL_REFUSE(1, "gemm_tc: M=%d N=%d K=%d", M, N, K);
   if (K % 8 || ldx % 8 || ldw % 8) RL_REFUSE(2, "gemm_tc: K=%d, ldx=%d, ldw=%d must be multiples of 8 (16-byte TMA rows)", K, ldx, ldw);
   if (swiglu && (N & 1)) RL_REFUSE(11, "gemm_tc: %d gate/up rows are not pairs", N);
@@ -483,7 +484,7 @@ RL_API int rl_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* out,
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)        \
       RL_REFUSE(10, "gemm_tc: cannot get %zu bytes of shared memory", smem);                                      \
     RL_LAUNCH_CHECK(rl_launch(kern, grid, NUM_THREADS, smem, stream, map_x, map_w, (TOUT*)out, ldo, M, N, K, vec_store,  \
-                              k_splits, bn, status, wait_test_role, (uint32_t)wait_test_ns));                         \
+                              k_splits, bn, status, wait_test_role, (uint32_t)wait_test_ns, act_alpha, act_limit));                         \
   } while (0)
   if (out_dtype == RL_BF16 && swiglu) RL_TC_LAUNCH(bf16, true);
   else if (out_dtype == RL_BF16) RL_TC_LAUNCH(bf16, false);

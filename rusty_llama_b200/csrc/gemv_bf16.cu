@@ -47,7 +47,7 @@ __device__ __forceinline__ void store_out<bf16>(bf16* p, float v) { *p = __float
 template <int NT, typename TO, bool SWIGLU>
 __global__ void __launch_bounds__(WARPS * 32)
 gemv_bf16_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w, int ldw, TO* __restrict__ out,
-                 int ldo, int M, int N, int K) {
+                 int ldo, int M, int N, int K, float act_alpha, float act_limit) {
   __shared__ float red[WARPS][NT * 128];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t4 = lane & 3;
@@ -123,7 +123,7 @@ gemv_bf16_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w
         usum += red[wq][iu];
       }
       const int col = (n0 >> 1) + pr;
-      if (col < (N >> 1) && m < M) store_out<TO>(out + (size_t)m * ldo + col, gsum * (1.0f / (1.0f + expf(-gsum))) * usum);
+      if (col < (N >> 1) && m < M) store_out<TO>(out + (size_t)m * ldo + col, gated_act(gsum, usum, act_alpha, act_limit));
     }
   } else {
     for (int e = tid; e < NT * 128; e += WARPS * 32) {
@@ -140,16 +140,16 @@ gemv_bf16_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w
 
 template <int NT>
 static int launch_gemv(const bf16* x, int ldx, const bf16* w, int ldw, void* out, int out_dtype, int ldo, int M,
-                       int N, int K, int swiglu, int k_splits, cudaStream_t stream) {
+                       int N, int K, int swiglu, float act_alpha, float act_limit, int k_splits, cudaStream_t stream) {
   const dim3 blocks((N + 15) / 16, k_splits);
   if (swiglu && out_dtype == RL_F32)
-    RL_LAUNCH_CHECK(rl_launch<false>(gemv_bf16_kernel<NT, float, true>, blocks, WARPS * 32, 0, stream, x, ldx, w, ldw, (float*)out, ldo, M, N, K));
+    RL_LAUNCH_CHECK(rl_launch<false>(gemv_bf16_kernel<NT, float, true>, blocks, WARPS * 32, 0, stream, x, ldx, w, ldw, (float*)out, ldo, M, N, K, act_alpha, act_limit));
   else if (swiglu)
-    RL_LAUNCH_CHECK(rl_launch<false>(gemv_bf16_kernel<NT, bf16, true>, blocks, WARPS * 32, 0, stream, x, ldx, w, ldw, (bf16*)out, ldo, M, N, K));
+    RL_LAUNCH_CHECK(rl_launch<false>(gemv_bf16_kernel<NT, bf16, true>, blocks, WARPS * 32, 0, stream, x, ldx, w, ldw, (bf16*)out, ldo, M, N, K, act_alpha, act_limit));
   else if (out_dtype == RL_F32)
-    RL_LAUNCH_CHECK(rl_launch<false>(gemv_bf16_kernel<NT, float, false>, blocks, WARPS * 32, 0, stream, x, ldx, w, ldw, (float*)out, ldo, M, N, K));
+    RL_LAUNCH_CHECK(rl_launch<false>(gemv_bf16_kernel<NT, float, false>, blocks, WARPS * 32, 0, stream, x, ldx, w, ldw, (float*)out, ldo, M, N, K, act_alpha, act_limit));
   else
-    RL_LAUNCH_CHECK(rl_launch<false>(gemv_bf16_kernel<NT, bf16, false>, blocks, WARPS * 32, 0, stream, x, ldx, w, ldw, (bf16*)out, ldo, M, N, K));
+    RL_LAUNCH_CHECK(rl_launch<false>(gemv_bf16_kernel<NT, bf16, false>, blocks, WARPS * 32, 0, stream, x, ldx, w, ldw, (bf16*)out, ldo, M, N, K, act_alpha, act_limit));
   return 0;
 }
 
@@ -159,7 +159,7 @@ RL_API int rl_gemv_bf16_max_rows() { return 64; }
 // k_splits > 1: the k range is cut into that many slices, each summed by blocks of its own; out is then
 // [k_splits][M][ldo] float32 partial results (more blocks in flight for matrices with few rows).
 RL_API int rl_gemv_bf16(const void* x, int ldx, const void* w, int ldw, void* out, int out_dtype, int ldo, int M,
-                        int N, int K, int swiglu, int k_splits, cudaStream_t stream) {
+                        int N, int K, int swiglu, float act_alpha, float act_limit, int k_splits, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) RL_REFUSE(1, "gemv_bf16: M=%d N=%d K=%d", M, N, K);
   if (M > 64) RL_REFUSE(2, "gemv_bf16: %d rows, this kernel takes at most 64", M);
   if (K % 8 || ldx % 8 || ldw % 8) RL_REFUSE(3, "gemv_bf16: K=%d, ldx=%d, ldw=%d must be multiples of 8 (16-byte loads)", K, ldx, ldw);
@@ -170,8 +170,8 @@ RL_API int rl_gemv_bf16(const void* x, int ldx, const void* w, int ldw, void* ou
   if (out_dtype != RL_F32 && out_dtype != RL_BF16) RL_REFUSE(5, "gemv_bf16: unknown output dtype %d", out_dtype);
   const bf16* xx = (const bf16*)x;
   const bf16* ww = (const bf16*)w;
-  if (M <= 8) return launch_gemv<1>(xx, ldx, ww, ldw, out, out_dtype, ldo, M, N, K, swiglu, k_splits, stream);
-  if (M <= 16) return launch_gemv<2>(xx, ldx, ww, ldw, out, out_dtype, ldo, M, N, K, swiglu, k_splits, stream);
-  if (M <= 32) return launch_gemv<4>(xx, ldx, ww, ldw, out, out_dtype, ldo, M, N, K, swiglu, k_splits, stream);
-  return launch_gemv<8>(xx, ldx, ww, ldw, out, out_dtype, ldo, M, N, K, swiglu, k_splits, stream);
+  if (M <= 8) return launch_gemv<1>(xx, ldx, ww, ldw, out, out_dtype, ldo, M, N, K, swiglu, act_alpha, act_limit, k_splits, stream);
+  if (M <= 16) return launch_gemv<2>(xx, ldx, ww, ldw, out, out_dtype, ldo, M, N, K, swiglu, act_alpha, act_limit, k_splits, stream);
+  if (M <= 32) return launch_gemv<4>(xx, ldx, ww, ldw, out, out_dtype, ldo, M, N, K, swiglu, act_alpha, act_limit, k_splits, stream);
+  return launch_gemv<8>(xx, ldx, ww, ldw, out, out_dtype, ldo, M, N, K, swiglu, act_alpha, act_limit, k_splits, stream);
 }

@@ -71,6 +71,8 @@ struct StreamBarriers {
 
 // A norm folded into this product (see the header); all pointers null: none.
 struct Fold {
+  // the activation of a gate/up product (gated_act of common.cuh): limit <= 0 is silu(gate) * up
+  float act_alpha, act_limit;
   // the norm comes BEFORE this product: its rows' sums of squares as [scale_blocks][8] shares, the row length
   // they were taken over, eps; the activations are x * w already
   const float* sumsq_in;
@@ -260,7 +262,7 @@ gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ 
           gate *= scale;
           up *= scale;
           const int m = (l >> 2) + 8 * hi, col = unit * (UNIT_ROWS / 2) + (l & 3);
-          if (m < M && col < (N >> 1)) store_out<TO>(out_slice + (size_t)m * ldo + col, gate * (1.0f / (1.0f + expf(-gate))) * up);
+          if (m < M && col < (N >> 1)) store_out<TO>(out_slice + (size_t)m * ldo + col, gated_act(gate, up, fold.act_alpha, fold.act_limit));
         }
       } else {
         const int l = e >> 2, c = e & 3;
@@ -513,9 +515,11 @@ static int launch_gemv_stream(const void* x, int ldx, const void* w, int ldw, vo
 }
 
 RL_API int rl_gemv_stream(const void* x, int ldx, const void* w, int ldw, void* out, int out_dtype, int ldo, int M, int N,
-                          int K, int swiglu, int k_slices, int* slices_used, int* status, int wait_test_role,
-                          unsigned int wait_test_ns, cudaStream_t stream) {
-  const Fold none = {};
+                          int K, int swiglu, float act_alpha, float act_limit, int k_slices, int* slices_used, int* status,
+                          int wait_test_role, unsigned int wait_test_ns, cudaStream_t stream) {
+  Fold none = {};
+  none.act_alpha = act_alpha;
+  none.act_limit = act_limit;
   return launch_gemv_stream(x, ldx, w, ldw, out, out_dtype, ldo, M, N, K, swiglu, k_slices, slices_used, status, wait_test_role,
                             wait_test_ns, none, nullptr, stream);
 }
@@ -557,9 +561,11 @@ RL_API int rl_gemv_stream_into_stream(const void* x, int ldx, const void* w, int
 // rl_gemv_stream_into_stream, every row's sums multiplied by 1 / sqrt(sum(shares) / norm_k + eps) before they are
 // stored or go through the activation.
 RL_API int rl_gemv_stream_scaled(const void* x, int ldx, const void* w, int ldw, void* out, int out_dtype, int ldo, int M, int N, int K,
-                                 int swiglu, const float* sumsq, int scale_blocks, int norm_k, float eps, int* status,
-                                 int wait_test_role, unsigned int wait_test_ns, cudaStream_t stream) {
+                                 int swiglu, float act_alpha, float act_limit, const float* sumsq, int scale_blocks, int norm_k, float eps,
+                                 int* status, int wait_test_role, unsigned int wait_test_ns, cudaStream_t stream) {
   Fold fold = {};
+  fold.act_alpha = act_alpha;
+  fold.act_limit = act_limit;
   fold.sumsq_in = sumsq;
   fold.scale_blocks = scale_blocks;
   fold.norm_k = norm_k;

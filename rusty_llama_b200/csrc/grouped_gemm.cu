@@ -5,16 +5,15 @@
 //                    matrix; with ACT it computes the gate and the up product together and writes silu(gate) * up
 //   head_linear_mma  out[t, h, :] = W[h] x[t, h, :] for every head h, optionally times sigmoid(gate[t, h, :])
 //
-// Both are the same tile loop: BM rows x 64 columns per block of four warps, k in slices of 64 through two stages of
-// shared memory filled by cp.async (rows and columns past the end, and the tail of k, are filled with zeros).  BM = 128
-// (each warp 32 rows x 64 columns) for the many rows of a prompt step, BM = 32 (each warp 32 rows x 16 columns) for the
-// few of a decode step, where the time goes into streaming each expert's matrix once.  k must be a multiple of 8 and
+// Both are the same tile loop: BM rows x BN columns per block, k in slices of 64 through two stages of shared memory
+// filled by cp.async (rows and columns past the end, and the tail of k, are filled with zeros).  128 x 128 with eight
+// warps (each 32 rows x 64 columns) for the many rows of a prompt step, 32 x 64 with four warps (each 32 rows x 16
+// columns) for the few of a decode step, where the time goes into streaming each expert's matrix once.  k must be a multiple of 8 and
 // all rows 16-byte aligned; the plain kernels take everything else.
 #include "common.cuh"
 
 RL_DEFINE_ERROR_TEXT()
 
-#define GG_BN 64
 #define GG_BK 64
 #define GG_STRIDE (GG_BK + 8)
 
@@ -40,17 +39,17 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
 }
 
 // The tile loop.  a_rows[r]: where row r of the tile starts (nullptr: a row of zeros).  w (and w2 with ACT): [N, K] with
-// rows ldw apart; columns n0 .. n0 + 63.  WM x WN warps; a warp holds MT x NT fragments of 16 x 8.
-template <int BM, int WM, int WN, bool ACT>
+// rows ldw apart; columns n0 .. n0 + BN - 1.  WM x WN warps; a warp holds MT x NT fragments of 16 x 8.
+template <int BM, int BN, int WM, int WN, bool ACT>
 struct Tile {
-  static constexpr int MT = BM / WM / 16, NT = GG_BN / WN / 8;
-  static constexpr size_t smem_bytes = (size_t)2 * (BM + (ACT ? 2 : 1) * GG_BN) * GG_STRIDE * sizeof(bf16);
+  static constexpr int MT = BM / WM / 16, NT = BN / WN / 8, THREADS = WM * WN * 32;
+  static constexpr size_t smem_bytes = (size_t)2 * (BM + (ACT ? 2 : 1) * BN) * GG_STRIDE * sizeof(bf16);
 
   __device__ static void run(const bf16* const* a_rows, const bf16* __restrict__ w, const bf16* __restrict__ w2, int ldw, int N, int K,
                              int n0, bf16* smem, float (&acc)[MT][NT][4], float (&acc2)[ACT ? MT : 1][ACT ? NT : 1][4]) {
     bf16* a_s = smem;                                    // [2][BM][STRIDE]
     bf16* w_s = a_s + (size_t)2 * BM * GG_STRIDE;        // [2][BN][STRIDE]
-    bf16* w2_s = w_s + (size_t)2 * GG_BN * GG_STRIDE;    // [2][BN][STRIDE] with ACT
+    bf16* w2_s = w_s + (size_t)2 * BN * GG_STRIDE;    // [2][BN][STRIDE] with ACT
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wm = warp / WN, wn = warp % WN;
 #pragma unroll
@@ -65,15 +64,15 @@ struct Tile {
     }
     auto load = [&](int stage, int k0) {
       bf16* as = a_s + (size_t)stage * BM * GG_STRIDE;
-      for (int c = tid; c < BM * (GG_BK / 8); c += 128) {
+      for (int c = tid; c < BM * (GG_BK / 8); c += THREADS) {
         const int r = c / (GG_BK / 8), k = k0 + (c % (GG_BK / 8)) * 8;
         const bf16* row = a_rows[r];
         const bool ok = row != nullptr && k < K;
         cp_async_16_zfill(as + (size_t)r * GG_STRIDE + (k - k0), ok ? row + k : w, ok);
       }
-      bf16* ws = w_s + (size_t)stage * GG_BN * GG_STRIDE;
-      bf16* ws2 = w2_s + (size_t)stage * GG_BN * GG_STRIDE;
-      for (int c = tid; c < GG_BN * (GG_BK / 8); c += 128) {
+      bf16* ws = w_s + (size_t)stage * BN * GG_STRIDE;
+      bf16* ws2 = w2_s + (size_t)stage * BN * GG_STRIDE;
+      for (int c = tid; c < BN * (GG_BK / 8); c += THREADS) {
         const int r = c / (GG_BK / 8), k = k0 + (c % (GG_BK / 8)) * 8;
         const bool ok = n0 + r < N && k < K;
         cp_async_16_zfill(ws + (size_t)r * GG_STRIDE + (k - k0), ok ? w + (size_t)(n0 + r) * ldw + k : w, ok);
@@ -94,8 +93,8 @@ struct Tile {
       }
       __syncthreads();
       const bf16* as = a_s + (size_t)st * BM * GG_STRIDE;
-      const bf16* ws = w_s + (size_t)st * GG_BN * GG_STRIDE;
-      const bf16* ws2 = w2_s + (size_t)st * GG_BN * GG_STRIDE;
+      const bf16* ws = w_s + (size_t)st * BN * GG_STRIDE;
+      const bf16* ws2 = w2_s + (size_t)st * BN * GG_STRIDE;
 #pragma unroll
       for (int kk = 0; kk < GG_BK / 16; ++kk) {
         uint32_t a[MT][4];
@@ -128,22 +127,22 @@ struct Tile {
 };
 
 // ---------------------------------------------------------------- the experts' products
-template <int BM, int WM, int WN, bool ACT, typename TO>
-__global__ void __launch_bounds__(128)
+template <int BM, int BN, int WM, int WN, bool ACT, typename TO>
+__global__ void __launch_bounds__(WM * WN * 32)
 moe_gemm_mma_kernel(const bf16* __restrict__ x, int ldx, const int* __restrict__ order, int gather_div, const bf16* __restrict__ w,
                     const bf16* __restrict__ w2, TO* __restrict__ out, int ldo, const int* __restrict__ tiles, int N, int K) {
-  using T = Tile<BM, WM, WN, ACT>;
+  using T = Tile<BM, BN, WM, WN, ACT>;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ const bf16* a_rows[BM];
   pdl_trigger();
   pdl_wait();
   if ((int)blockIdx.y >= tiles[0]) return;
   const int e = tiles[1 + 3 * blockIdx.y], r0 = tiles[2 + 3 * blockIdx.y], rows = tiles[3 + 3 * blockIdx.y];
-  for (int r = threadIdx.x; r < BM; r += 128)
+  for (int r = threadIdx.x; r < BM; r += T::THREADS)
     a_rows[r] = r < rows ? x + (size_t)(order ? order[r0 + r] / gather_div : r0 + r) * ldx : nullptr;
   __syncthreads();
   float acc[T::MT][T::NT][4], acc2[ACT ? T::MT : 1][ACT ? T::NT : 1][4];
-  const int n0 = blockIdx.x * GG_BN;
+  const int n0 = blockIdx.x * BN;
   T::run(a_rows, w + (size_t)e * N * K, ACT ? w2 + (size_t)e * N * K : nullptr, K, N, K, n0, reinterpret_cast<bf16*>(smem_raw), acc, acc2);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wm = warp / WN, wn = warp % WN, g = lane >> 2, t4 = lane & 3;
 #pragma unroll
@@ -171,26 +170,32 @@ RL_API int rl_moe_gemm_mma(const void* x, int ldx, const int* order, int gather_
   if (max_tiles > 65535) RL_REFUSE(2, "moe_gemm_mma: %d row tiles exceed the grid", max_tiles);
   if (K % 8 || ldx % 8) RL_REFUSE(3, "moe_gemm_mma: k = %d or a row stride of %d elements breaks 16-byte alignment", K, ldx);
   if (tile_rows != 32 && tile_rows != 128) RL_REFUSE(4, "moe_gemm_mma: row tiles of %d, this kernel is built for 32 and 128", tile_rows);
-  dim3 grid((N + GG_BN - 1) / GG_BN, max_tiles);
-#define RL_GG(BM, WM, WN, ACT, TO)                                                                                                  \
+#define RL_GG(BM, BN, WM, WN, ACT, TO)                                                                                              \
   do {                                                                                                                              \
-    auto kern = moe_gemm_mma_kernel<BM, WM, WN, ACT, TO>;                                                                           \
-    const size_t smem = Tile<BM, WM, WN, ACT>::smem_bytes;                                                                          \
+    auto kern = moe_gemm_mma_kernel<BM, BN, WM, WN, ACT, TO>;                                                                       \
+    const size_t smem = Tile<BM, BN, WM, WN, ACT>::smem_bytes;                                                                      \
+    dim3 grid((N + BN - 1) / BN, max_tiles);                                                                                        \
     if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)      \
       RL_REFUSE(5, "moe_gemm_mma: cannot get %zu bytes of shared memory", smem);                                                    \
-    RL_LAUNCH_CHECK(rl_launch<false>(kern, grid, 128, smem, stream, (const bf16*)x, ldx, order, gather_div, (const bf16*)w,         \
+    RL_LAUNCH_CHECK(rl_launch<false>(kern, grid, WM * WN * 32, smem, stream, (const bf16*)x, ldx, order, gather_div, (const bf16*)w, \
                                      (const bf16*)w2, (TO*)out, ldo, tiles, N, K));                                                 \
     return 0;                                                                                                                       \
   } while (0)
   const bool act = w2 != nullptr;
   if (tile_rows == 128) {
-    if (act && out_dtype == RL_BF16) RL_GG(128, 4, 1, true, bf16);
-    if (!act && out_dtype == RL_F32) RL_GG(128, 4, 1, false, float);
-    if (!act && out_dtype == RL_BF16) RL_GG(128, 4, 1, false, bf16);
+    // 128 x 128 tiles for eight warps (32 rows x 64 columns each); a matrix of up to 64 rows keeps the narrow tile
+    if (N > 64) {
+      if (act && out_dtype == RL_BF16) RL_GG(128, 128, 4, 2, true, bf16);
+      if (!act && out_dtype == RL_F32) RL_GG(128, 128, 4, 2, false, float);
+      if (!act && out_dtype == RL_BF16) RL_GG(128, 128, 4, 2, false, bf16);
+    }
+    if (act && out_dtype == RL_BF16) RL_GG(128, 64, 4, 1, true, bf16);
+    if (!act && out_dtype == RL_F32) RL_GG(128, 64, 4, 1, false, float);
+    if (!act && out_dtype == RL_BF16) RL_GG(128, 64, 4, 1, false, bf16);
   } else {
-    if (act && out_dtype == RL_BF16) RL_GG(32, 1, 4, true, bf16);
-    if (!act && out_dtype == RL_F32) RL_GG(32, 1, 4, false, float);
-    if (!act && out_dtype == RL_BF16) RL_GG(32, 1, 4, false, bf16);
+    if (act && out_dtype == RL_BF16) RL_GG(32, 64, 1, 4, true, bf16);
+    if (!act && out_dtype == RL_F32) RL_GG(32, 64, 1, 4, false, float);
+    if (!act && out_dtype == RL_BF16) RL_GG(32, 64, 1, 4, false, bf16);
   }
 #undef RL_GG
   RL_REFUSE(6, "moe_gemm_mma: unsupported output type %d (activation %d)", out_dtype, (int)act);
@@ -198,17 +203,17 @@ RL_API int rl_moe_gemm_mma(const void* x, int ldx, const int* order, int gather_
 
 // ---------------------------------------------------------------- one product per head
 // x, out, gate: element (t, h, i) at base + t * ld + h * head_stride + i.  w: [H, N, K] dense.
-template <int BM, int WM, int WN, bool GATE>
-__global__ void __launch_bounds__(128)
+template <int BM, int BN, int WM, int WN, bool GATE>
+__global__ void __launch_bounds__(WM * WN * 32)
 head_linear_mma_kernel(const bf16* __restrict__ x, int ldx, int xh, const bf16* __restrict__ w, bf16* __restrict__ out, int ldo, int oh,
                        const bf16* __restrict__ gate, int ldg, int gh, int M, int N, int K) {
-  using T = Tile<BM, WM, WN, false>;
+  using T = Tile<BM, BN, WM, WN, false>;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ const bf16* a_rows[BM];
   pdl_trigger();
   pdl_wait();
-  const int h = blockIdx.z, m0 = blockIdx.y * BM, n0 = blockIdx.x * GG_BN;
-  for (int r = threadIdx.x; r < BM; r += 128) a_rows[r] = m0 + r < M ? x + (size_t)(m0 + r) * ldx + (size_t)h * xh : nullptr;
+  const int h = blockIdx.z, m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  for (int r = threadIdx.x; r < BM; r += T::THREADS) a_rows[r] = m0 + r < M ? x + (size_t)(m0 + r) * ldx + (size_t)h * xh : nullptr;
   __syncthreads();
   float acc[T::MT][T::NT][4], none[1][1][4];
   T::run(a_rows, w + (size_t)h * N * K, nullptr, K, N, K, n0, reinterpret_cast<bf16*>(smem_raw), acc, none);
@@ -243,20 +248,23 @@ RL_API int rl_head_linear_mma(const void* x, int ldx, int xh, const void* w, voi
   const int BM = big ? 128 : 32;
   const int gy = (M + BM - 1) / BM;
   if (gy > 65535 || H > 65535) RL_REFUSE(3, "head_linear_mma: %d rows or %d heads exceed the grid", M, H);
-  dim3 grid((N + GG_BN - 1) / GG_BN, gy, H);
-#define RL_HL(BM, WM, WN, G)                                                                                                        \
+#define RL_HL(BM, BN, WM, WN, G)                                                                                                    \
   do {                                                                                                                              \
-    auto kern = head_linear_mma_kernel<BM, WM, WN, G>;                                                                              \
-    const size_t smem = Tile<BM, WM, WN, false>::smem_bytes;                                                                        \
+    auto kern = head_linear_mma_kernel<BM, BN, WM, WN, G>;                                                                          \
+    const size_t smem = Tile<BM, BN, WM, WN, false>::smem_bytes;                                                                    \
+    dim3 grid((N + BN - 1) / BN, gy, H);                                                                                            \
     if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)      \
       RL_REFUSE(5, "head_linear_mma: cannot get %zu bytes of shared memory", smem);                                                 \
-    RL_LAUNCH_CHECK(rl_launch<false>(kern, grid, 128, smem, stream, (const bf16*)x, ldx, xh, (const bf16*)w, (bf16*)out, ldo, oh,   \
+    RL_LAUNCH_CHECK(rl_launch<false>(kern, grid, WM * WN * 32, smem, stream, (const bf16*)x, ldx, xh, (const bf16*)w, (bf16*)out,  \
+                                     ldo, oh,                                                                                       \
                                      (const bf16*)gate, ldg, gh, M, N, K));                                                         \
     return 0;                                                                                                                       \
   } while (0)
-  if (big && gate) RL_HL(128, 4, 1, true);
-  if (big) RL_HL(128, 4, 1, false);
-  if (gate) RL_HL(32, 1, 4, true);
-  RL_HL(32, 1, 4, false);
+  if (big && N > 64 && gate) RL_HL(128, 128, 4, 2, true);
+  if (big && N > 64) RL_HL(128, 128, 4, 2, false);
+  if (big && gate) RL_HL(128, 64, 4, 1, true);
+  if (big) RL_HL(128, 64, 4, 1, false);
+  if (gate) RL_HL(32, 64, 1, 4, true);
+  RL_HL(32, 64, 1, 4, false);
 #undef RL_HL
 }

@@ -201,7 +201,7 @@ RL_API int rl_head_linear(const void* x, int ldx, int xh, const void* w, long lo
 // One warp per (token, head).  A cached row is [rank latent | rot shared key part]; the query row has the same
 // layout; the result is the probability-weighted sum of the latent parts.  Keys in groups of 32 from position 0
 // (or from the first key inside `window`, if one is given), online softmax that starts from the sink.
-#define LA_MAX_PER_LANE 16  // latent sizes up to 512
+#define LA_MAX_PER_LANE 32  // latent sizes up to 1024
 
 template <typename T>
 __global__ void latent_attn_kernel(const T* __restrict__ q_cat, const T* __restrict__ pages,

@@ -200,16 +200,17 @@ def kernel_table(z: dict, T: int, batch: int, ctx: int, peaks: dict) -> Dict[str
         us = mb._time(lambda i: ops.moe_router(x, wr, bias, E, top), 1, **it)
         note(f"{tag}_router", us, (E + 1) * d * 4 + rows * d * 2, 0)
         ids, wts, gate = ops.moe_router(x, wr, bias, E, top)
-        us = mb._time(lambda i: ops.moe_plan(ids, E), 1, **it)
+        us = mb._time(lambda i: ops.moe_plan(ids, E, 128 if rows * top >= 64 * E else 32), 1, **it)
         note(f"{tag}_plan", us, rows * top * 12, 0)
-        order, place, tiles, max_tiles = ops.moe_plan(ids, E)
+        tile_rows = 128 if rows * top >= 64 * E else 32  # as `RoutedExperts.forward` chooses
+        order, place, tiles, max_tiles = ops.moe_plan(ids, E, tile_rows)
         used = int(torch.unique(ids).numel())
-        us = mb._time(lambda i: ops.moe_gemm(x, wg, tiles, max_tiles, rows * top, order=order, gather_div=top, w2=wu), 1, **it)
+        us = mb._time(lambda i: ops.moe_gemm(x, wg, tiles, max_tiles, rows * top, order=order, gather_div=top, w2=wu, tile_rows=tile_rows), 1, **it)
         note(f"{tag}_experts_gate_up", us, (2 * used * eff * d + rows * d + rows * top * eff) * 2, 4.0 * rows * top * eff * d)
-        h = ops.moe_gemm(x, wg, tiles, max_tiles, rows * top, order=order, gather_div=top, w2=wu)
-        us = mb._time(lambda i: ops.moe_gemm(h, wd, tiles, max_tiles, rows * top, out_dtype=torch.float32), 1, **it)
+        h = ops.moe_gemm(x, wg, tiles, max_tiles, rows * top, order=order, gather_div=top, w2=wu, tile_rows=tile_rows)
+        us = mb._time(lambda i: ops.moe_gemm(h, wd, tiles, max_tiles, rows * top, out_dtype=torch.float32, tile_rows=tile_rows), 1, **it)
         note(f"{tag}_experts_down", us, (used * eff * d + rows * top * eff) * 2 + rows * top * d * 4, 2.0 * rows * top * eff * d)
-        y = ops.moe_gemm(h, wd, tiles, max_tiles, rows * top, out_dtype=torch.float32)
+        y = ops.moe_gemm(h, wd, tiles, max_tiles, rows * top, out_dtype=torch.float32, tile_rows=tile_rows)
         shared = torch.randn(rows, d, device=dev, dtype=bf)
         us = mb._time(lambda i: ops.moe_combine(y, place, wts, shared, gate), 1, **it)
         note(f"{tag}_experts_sum", us, rows * top * d * 4 + rows * d * 6, 0)

@@ -74,20 +74,21 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     return ops.gemm_tc(x, w, out_dtype)
 
 
-def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
-    """h[M, ff] = silu(x . Wg^T) * (x . Wu^T) in one kernel, for bfloat16.
+def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, act=None) -> torch.Tensor:
+    """h[M, ff] = silu(x . Wg^T) * (x . Wu^T) in one kernel, for bfloat16.  act = (alpha, limit) puts the activation with
+    limits in silu's place: g s(alpha g) (u + 1) with g = min(x . Wg^T, limit), u = clamp(x . Wu^T, -limit, limit).
 
     w_gate_up[2 ff, K] holds the rows of Wg and Wu alternately (row 2i is gate i, row 2i + 1 is up i);
     the product's 32-bit sums go through the activation before anything is rounded or stored."""
     if x.dtype != torch.bfloat16 or w_gate_up.dtype != torch.bfloat16:
         raise KernelError(f"linear_swiglu: bfloat16 only, got {x.dtype} x {w_gate_up.dtype}")
     if _odd(x, w_gate_up):
-        return ops.gemm_bf16_any(x, w_gate_up, torch.bfloat16, swiglu=True)
+        return ops.gemm_bf16_any(x, w_gate_up, torch.bfloat16, swiglu=True, act=act)
     if x.shape[0] <= STREAM_MAX_ROWS:
         if _streams(x.shape[0], x.shape[1], whole=True):
-            return ops.gemv_stream(x, w_gate_up, torch.bfloat16, swiglu=True)
-        return ops.gemv_bf16(x, w_gate_up, torch.bfloat16, swiglu=True)
-    return ops.gemm_tc(x, w_gate_up, torch.bfloat16, swiglu=True)
+            return ops.gemv_stream(x, w_gate_up, torch.bfloat16, swiglu=True, act=act)
+        return ops.gemv_bf16(x, w_gate_up, torch.bfloat16, swiglu=True, act=act)
+    return ops.gemm_tc(x, w_gate_up, torch.bfloat16, swiglu=True, act=act)
 
 
 # resident blocks of the register-streaming kernel per SM: its splits of k aim at filling the GPU once

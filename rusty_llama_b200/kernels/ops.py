@@ -493,8 +493,17 @@ def gemm_f32(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = Non
     return out
 
 
+def _act(act):
+    """(alpha, limit) of a gate/up product's activation as the launchers take it: None is silu(gate) * up."""
+    if act is None:
+        return c_float(1.0), c_float(0.0)
+    alpha, limit = act
+    _need(limit > 0, f"a gated activation with limits needs a positive limit, got {limit}")
+    return c_float(alpha), c_float(limit)
+
+
 def gemm_bf16_any(
-    x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, swiglu: bool = False
+    x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, swiglu: bool = False, act=None,
 ) -> torch.Tensor:
     """out[M, N] = x[M, K] . w[N, K]^T for bfloat16 operands of any k and alignment, 32-bit sums on the
     CUDA cores: the slow kernel behind the shapes that the 16-byte-row kernels refuse.
@@ -510,7 +519,7 @@ def gemm_bf16_any(
     lib = build.load("gemm_f32")
     rc = lib.rl_gemm_bf16_any(
         _p(x), c_int(ldx), _p(w), c_int(ldw), _p(out), c_int(_dt(out, "gemm_bf16_any out")), c_int(out.shape[1]),
-        c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), _stream(),
+        c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), *_act(act), _stream(),
     )
     _check(lib, rc, "gemm_bf16_any")
     return out
@@ -518,9 +527,11 @@ def gemm_bf16_any(
 
 def gemv_bf16(
     x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None,
-    swiglu: bool = False, k_splits: int = 1,
+    swiglu: bool = False, k_splits: int = 1, act=None,
 ) -> torch.Tensor:
     """out[M, N] = x[M, K] . w[N, K]^T for M <= 64 rows, bfloat16 in, 32-bit accumulate.
+    (act, here and in the other products with `swiglu`: None for silu(gate) * up, or (alpha, limit) for
+    g s(alpha g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit).)
 
     swiglu: w's rows alternate gate and up; out[M, N/2] = silu(gate) * up, from the 32-bit sums.
     k_splits > 1: returns float32 [k_splits, M, N], one partial sum per slice of k, for a consumer
@@ -549,7 +560,7 @@ def gemv_bf16(
     lib = build.load("gemv_bf16")
     rc = lib.rl_gemv_bf16(
         _p(x), c_int(ldx), _p(w), c_int(ldw), _p(out), c_int(_dt(out, "gemv_bf16 out")), c_int(ldo),
-        c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), c_int(k_splits), _stream(),
+        c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), *_act(act), c_int(k_splits), _stream(),
     )
     _check(lib, rc, "gemv_bf16")
     return out
@@ -606,7 +617,7 @@ def gemv_stream_into_stream(
 
 def gemv_stream(
     x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None,
-    swiglu: bool = False, k_splits: int = 1, row_scale=None,
+    swiglu: bool = False, k_splits: int = 1, row_scale=None, act=None,
 ) -> torch.Tensor:
     """out[M, N] = x[M, K] . w[N, K]^T for M <= 16 rows: the persistent weight-streaming kernel of
     decode steps (bulk copies into a ring of shared memory, one block per SM).
@@ -645,13 +656,13 @@ def gemv_stream(
         _need(k_splits == 1 and slices == 1 and sumsq.numel() >= blocks * 8, "gemv_stream: a row scale goes with whole sums and needs its shares")
         rc = lib.rl_gemv_stream_scaled(
             _p(x), c_int(ldx), _p(w), c_int(ldw), _p(out), c_int(_dt(out, "gemv_stream out")), c_int(ldo), c_int(M), c_int(N), c_int(K),
-            c_int(1 if swiglu else 0), _p(sumsq), c_int(blocks), c_int(norm_k), c_float(eps), _p(status), *_wt(), _stream(),
+            c_int(1 if swiglu else 0), *_act(act), _p(sumsq), c_int(blocks), c_int(norm_k), c_float(eps), _p(status), *_wt(), _stream(),
         )
         _check(lib, rc, "gemv_stream")
         return out
     rc = lib.rl_gemv_stream(
         _p(x), c_int(ldx), _p(w), c_int(ldw), _p(out), c_int(_dt(out, "gemv_stream out")), c_int(ldo),
-        c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), c_int(k_splits), ctypes.byref(used), _p(status), *_wt(), _stream(),
+        c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), *_act(act), c_int(k_splits), ctypes.byref(used), _p(status), *_wt(), _stream(),
     )
     _check(lib, rc, "gemv_stream")
     _need(used.value == slices, f"gemv_stream: kernel used {used.value} slices, the wrapper planned {slices}")
@@ -723,7 +734,7 @@ def tc_status_check() -> None:
 
 def gemm_tc(
     x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None,
-    swiglu: bool = False, k_splits: int = 1, tile_n: int = 0,
+    swiglu: bool = False, k_splits: int = 1, tile_n: int = 0, act=None,
 ) -> torch.Tensor:
     """out[M, N] = x[M, K] . w[N, K]^T on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory).
 
@@ -757,7 +768,7 @@ def gemm_tc(
     lib = build.load("gemm_tc")
     rc = lib.rl_gemm_tc(
         _p(x), c_int(ldx), _p(w), c_int(ldw), _p(out), c_int(_dt(out, "gemm_tc out")), c_int(ldo),
-        c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), c_int(k_splits), ctypes.byref(used), c_int(tile_n), _p(status), *_wt(), _stream(),
+        c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0), *_act(act), c_int(k_splits), ctypes.byref(used), c_int(tile_n), _p(status), *_wt(), _stream(),
     )
     _check(lib, rc, "gemm_tc")
     if k_splits > 1:

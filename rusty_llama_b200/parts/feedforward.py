@@ -18,8 +18,8 @@ class GatedMLP(FeedForward):
     (src/model.rs:1336-1345, src/backend/cpu.rs:435-440).
 
     activation "clamped_swish" (params `limit`, `alpha`): f = W_down (g s(alpha g) (u + 1)) with g = min(W_gate x, limit),
-    u = clamp(W_up x, -limit, limit), s the logistic function; its gate and up halves follow each other in both precisions
-    and a kernel of its own applies the activation.
+    u = clamp(W_up x, -limit, limit), s the logistic function; in bfloat16 the product's kernel applies it as it does silu,
+    in 32-bit a kernel of its own.
 
     params: hidden_size, intermediate_size, activation ("silu" or "clamped_swish"),
             names (optional: the three tensors' names after the prefix, keys gate up down).
@@ -54,7 +54,7 @@ class GatedMLP(FeedForward):
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         p = self.prefix
         gate, up = tensors[p + self.names["gate"]], tensors[p + self.names["up"]]
-        self.fused = self.rt.dtype == torch.bfloat16 and self.activation == "silu"
+        self.fused = self.rt.dtype == torch.bfloat16
         if self.fused:
             self.w_gate_up = torch.stack([gate, up], dim=1).reshape(2 * self.ff, self.d).contiguous()
         else:
@@ -62,11 +62,11 @@ class GatedMLP(FeedForward):
         self.w_down = tensors[p + self.names["down"]].contiguous()
 
     def gated_weights(self):
-        return (self.w_gate_up, self.w_down) if self.fused else None
+        return (self.w_gate_up, self.w_down) if (self.fused and self.activation == "silu") else None
 
     def forward(self, xn: torch.Tensor, step) -> torch.Tensor:
         if self.fused:
-            h = linear_swiglu(xn, self.w_gate_up)
+            h = linear_swiglu(xn, self.w_gate_up, act=(self.alpha, self.limit) if self.activation == "clamped_swish" else None)
         elif self.activation == "clamped_swish":
             h = ops.clamped_glu(linear(xn, self.w_gate_up), self.alpha, self.limit)
         else:

@@ -56,8 +56,8 @@ class LatentAttention(Mixer):
         self.names = dict(_NAMES, **dict(spec.params.get("names", {})))
         if min(self.H, self.rank, self.vdim) <= 0 or self.dim < 0 or self.rot < 0 or self.dim + self.rot == 0:
             raise ConfigError(f"latent_attention: sizes heads={self.H} dim={self.dim} rot_dim={self.rot} vdim={self.vdim} kv_rank={self.rank}")
-        if self.rank > 512:
-            raise ConfigError(f"latent_attention: kv_rank {self.rank} is above 512, the most the attention kernels built here take")
+        if self.rank > 1024:
+            raise ConfigError(f"latent_attention: kv_rank {self.rank} is above 1024, the most the attention kernels built here take")
         pos_spec = self._param("position")
         if not isinstance(pos_spec, PartSpec):
             raise ConfigError("latent_attention: 'position' must be a PartSpec")
