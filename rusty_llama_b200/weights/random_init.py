@@ -95,4 +95,9 @@ def random_model(config_json: Mapping, seed: int, dtype="bfloat16", device="cuda
         t = random_tensor(name, info, seed, stored, std, norm_jitter, device=runtime.device)
         placed[name] = place(t, info, runtime)
     model.load(placed)
+    if runtime.device.type == "cuda":
+        # Gigabytes of random numbers are still being drawn when this returns, and the first step's kernels would be
+        # queued behind them: a kernel that starts early and waits for its predecessor with a bounded wait (a second)
+        # would give up on a large model.  Wait here instead.
+        torch.cuda.synchronize(runtime.device)
     return model
