@@ -27,7 +27,7 @@ def main(argv=None) -> int:
     ap.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for the <step>.f32 files")
-    ap.add_argument("--max-tokens", type=int, required=True, help="positions live requests hold at most, each rounded up to 64")
+    ap.add_argument("--max-tokens", type=int, required=True, help="tokens that live requests hold at most (room for each request's last, partly filled page is added)")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 
@@ -36,8 +36,11 @@ def main(argv=None) -> int:
     from .engine import StepEntry
 
     os.makedirs(args.out, exist_ok=True)
-    max_seqs = max(1, (args.max_tokens + PAGE_SIZE - 1) // PAGE_SIZE)
-    llm = load(args.model, dtype=args.dtype, device=args.device, max_tokens=args.max_tokens, max_seqs=max_seqs)
+    # --max-tokens counts the tokens that live requests hold, not the room a page leaves unused: every live request may
+    # waste up to a page less one position, and there may be as many live requests as tokens (at most 1024 are planned for)
+    max_seqs = max(1, min(args.max_tokens, 1024))
+    positions = args.max_tokens + (PAGE_SIZE - 1) * max_seqs
+    llm = load(args.model, dtype=args.dtype, device=args.device, max_tokens=positions, max_seqs=max_seqs)
     slots: Dict[str, int] = {}
     for line in sys.stdin:
         line = line.strip()

@@ -208,6 +208,11 @@ def test_trace_replay_and_command_line(models, dtype, tmp_path):
                 got["y"].append(out[1:2])
         check(np.concatenate(got["x"]), ref["a"], dtype, "cut and batched")
         check(np.concatenate(got["y"]), ref["b"], dtype, "the short one")
+        # forty requests of two tokens each: far fewer tokens than --max-tokens, but forty pages
+        many = [tokens(cfg, 2, 100 + i) for i in range(40)]
+        out = run.step([(f"m{i}", t, [1]) for i, t in enumerate(many)], end=[f"m{i}" for i in range(40)])
+        for i, t in enumerate(many):
+            check(out[i : i + 1], pv.forward(cfg, w, t)[1:], dtype, f"short request {i}")
     finally:
         run.close()
     if dtype == "float32":
