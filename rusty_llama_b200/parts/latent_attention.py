@@ -6,7 +6,6 @@ from typing import Dict, Mapping
 
 import torch
 
-from ..config.rope_scaling import magnitude
 from ..errors import ConfigError
 from ..kernels import ops
 from ..kernels.device import sm_count
