@@ -92,8 +92,9 @@ class KVGroup:
         # zero-filled once: a page that was never written holds finite values, which the
         # attention kernels rely on when they multiply masked scores by unread rows
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        # a need without values (one latent row per position, from which the mixer makes keys and values) has no value pages
-        self.v = torch.zeros(shape, dtype=dtype, device=device) if need.values else None
+        # a need without values (one latent row per position, from which the mixer makes keys and values) has no value pages;
+        # a value row may have another size than a key row
+        self.v = torch.zeros(shape[:-1] + (need.value_dim or need.head_dim,), dtype=dtype, device=device) if need.values else None
         self.pages: Dict[int, List[int]] = {}  # slot -> page id per page index (-1: given back)
         self.first_held: Dict[int, int] = {}  # slot -> lowest page index still held
         # the same page lists as one matrix [slot, page index] (0 where nothing is held), kept in
@@ -108,7 +109,7 @@ class KVGroup:
         self.table[slot, index] = max(page, 0)
 
     def bytes(self) -> int:
-        return (2 if self.v is not None else 1) * self.k.numel() * self.k.element_size()
+        return (self.k.numel() + (0 if self.v is None else self.v.numel())) * self.k.element_size()
 
     def first_needed_page(self, next_pos: int) -> int:
         """Lowest page index that a query at `next_pos` or later can still read."""
@@ -127,8 +128,14 @@ class StateGroup:
         return self.state.numel() * self.state.element_size()
 
 
+def _row_numbers(need: KVNeed) -> int:
+    """Numbers that one cached position of one run costs: a key row and, if there are values, a value row per kv head."""
+    return need.num_kv_heads * (need.head_dim + ((need.value_dim or need.head_dim) if need.values else 0))
+
+
 class Cache:
-    """needs: for each run of the schedule that owns cache storage, (run index, KVNeed | StateNeed).
+    """needs: for each run of the schedule that owns cache storage, (run index, KVNeed | StateNeed | a tuple of those:
+    `view(run)` is then a tuple of views in the same order).
     max_tokens: positions that can be held at once, each sequence rounded up to PAGE_SIZE.
     max_seqs: sequences that can be open at once."""
 
@@ -147,18 +154,25 @@ class Cache:
         self.n_pages = (max_tokens + PAGE_SIZE - 1) // PAGE_SIZE
         self.max_tokens = self.n_pages * PAGE_SIZE
         self.max_seqs = max_seqs
-        by_need: Dict[object, List[int]] = {}
+        by_need: Dict[object, List[object]] = {}
+        self._several: Dict[int, int] = {}  # run -> how many needs it named, for the runs that named a tuple
         for run, need in needs:
-            if not isinstance(need, (KVNeed, StateNeed)):
-                raise CacheError(f"run {run} asks for {need!r}, which is neither a KVNeed nor a StateNeed")
-            by_need.setdefault(need, []).append(run)
+            if isinstance(need, (tuple, list)):
+                self._several[run] = len(need)
+                keyed = [((run, i), n) for i, n in enumerate(need)]
+            else:
+                keyed = [(run, need)]
+            for key, n in keyed:
+                if not isinstance(n, (KVNeed, StateNeed)):
+                    raise CacheError(f"run {run} asks for {n!r}, which is neither a KVNeed nor a StateNeed")
+                by_need.setdefault(n, []).append(key)
         if self.device.type == "cuda":
             # say so before allocating, with the numbers, instead of running out of memory half-way
             asked = 0
             for need, runs in by_need.items():
                 if isinstance(need, KVNeed):
                     size = torch.empty((), dtype=need.dtype or dtype).element_size()
-                    asked += (2 if need.values else 1) * len(runs) * self.n_pages * need.num_kv_heads * PAGE_SIZE * need.head_dim * size
+                    asked += len(runs) * self.n_pages * PAGE_SIZE * _row_numbers(need) * size
                 else:
                     n = torch.empty((), dtype=need.dtype).element_size() * max_seqs * len(runs)
                     for s in need.shape:
@@ -172,7 +186,7 @@ class Cache:
                     f"ask for fewer positions (max_tokens)")
         self.kv_groups: List[KVGroup] = []
         self.state_groups: List[StateGroup] = []
-        self._where: Dict[int, Tuple[str, int, int]] = {}  # run -> (family, group index, index in group)
+        self._where: Dict[object, Tuple[str, int, int]] = {}  # run, or (run, index of the need) -> (family, group index, index in group)
         for need, runs in by_need.items():
             if isinstance(need, KVNeed):
                 self.kv_groups.append(KVGroup(need, runs, self.n_pages, dtype, self.device, max_seqs))
@@ -332,14 +346,21 @@ class Cache:
         return table
 
     # ------------------------------------------------------------------ views
-    def where(self, run: int) -> Tuple[str, int, int]:
+    def owns(self, run: int) -> bool:
+        """Whether the run of the schedule has cache storage of its own."""
+        return run in self._where or run in self._several
+
+    def where(self, run) -> Tuple[str, int, int]:
         try:
             return self._where[run]
         except KeyError:
             raise CacheError(f"run {run} of the schedule owns no cache storage") from None
 
-    def view(self, run: int, tables: Optional[Sequence[torch.Tensor]] = None):
-        """The storage of one run.  tables[g]: this step's device block table of kv group g."""
+    def view(self, run, tables: Optional[Sequence[torch.Tensor]] = None):
+        """The storage of one run (a tuple of views for a run that named several needs).  tables[g]: this step's device
+        block table of kv group g."""
+        if run in self._several:
+            return tuple(self.view((run, i), tables) for i in range(self._several[run]))
         family, gi, j = self.where(run)
         if family == "kv":
             g = self.kv_groups[gi]

@@ -430,13 +430,13 @@ RL_API int rl_clamped_glu(const void* gate_up, void* h, int act_dtype, int n_tok
 
 // ---------------------------------------------------------------- a normed sublayer result, the residual sum, the next norm
 // For a layer that norms what its sublayer returns before adding it (and norms the stream again for the next sublayer):
-//   s = delta[0][t] + delta[1][t] + ...                         (32-bit, in this order)
+//   s = delta[0][t] + delta[1][t] + ... (+ bias)                 (32-bit, in this order; bias: a row of d numbers or none)
 //   v = x[t] + s / sqrt(mean(s^2) + eps_d) * wd                 x[t] = v
 //   if w: out[t] = v / sqrt(mean(v^2) + eps) * w
 // One block per row, the row in shared memory between the passes; every sum in the block's fixed order.
 template <typename TA, typename TW, typename TD, bool VEC>
 __global__ void normed_add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_parts, long long part_stride,
-                                          const TW* __restrict__ wd, float eps_d, const TW* __restrict__ w, float eps,
+                                          const float* __restrict__ bias, const TW* __restrict__ wd, float eps_d, const TW* __restrict__ w, float eps,
                                           TA* __restrict__ out, const int* __restrict__ rows, int d, int write_x) {
   extern __shared__ __align__(16) float row[];
   __shared__ float red[32];
@@ -456,6 +456,10 @@ __global__ void normed_add_rmsnorm_kernel(float* __restrict__ x, const TD* __res
 #pragma unroll
         for (int e = 0; e < 4; ++e) s[e] += dv[e];
       }
+      if (bias != nullptr) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[e] += bias[i + e];
+      }
       store4<float>(row + i, s);
 #pragma unroll
       for (int e = 0; e < 4; ++e) ss += s[e] * s[e];
@@ -464,6 +468,7 @@ __global__ void normed_add_rmsnorm_kernel(float* __restrict__ x, const TD* __res
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
       float s = 0.f;
       for (int p = 0; p < n_parts; ++p) s += to_f32(delta[(size_t)p * part_stride + (size_t)t * d + i]);
+      if (bias != nullptr) s += bias[i];
       row[i] = s;
       ss += s * s;
     }
@@ -508,7 +513,7 @@ __global__ void normed_add_rmsnorm_kernel(float* __restrict__ x, const TD* __res
   }
 }
 
-RL_API int rl_normed_add_rmsnorm(float* x, const void* delta, int delta_dtype, int n_parts, long long part_stride, const void* wd,
+RL_API int rl_normed_add_rmsnorm(float* x, const void* delta, int delta_dtype, int n_parts, long long part_stride, const float* bias, const void* wd,
                                  float eps_d, const void* w, int w_dtype, float eps, void* out, int act_dtype, const int* rows,
                                  int n_rows, int d, int write_x, cudaStream_t stream) {
   if (n_rows <= 0 || d <= 0 || n_parts <= 0 || delta == nullptr || wd == nullptr)
@@ -524,10 +529,10 @@ RL_API int rl_normed_add_rmsnorm(float* x, const void* delta, int delta_dtype, i
   do {                                                                                                                          \
     if (vec)                                                                                                                    \
       RL_LAUNCH_CHECK(rl_launch(normed_add_rmsnorm_kernel<TA, TW, TD, true>, n_rows, th, smem, stream, x, (const TD*)delta,    \
-                                n_parts, part_stride, (const TW*)wd, eps_d, (const TW*)w, eps, (TA*)out, rows, d, write_x));    \
+                                n_parts, part_stride, bias, (const TW*)wd, eps_d, (const TW*)w, eps, (TA*)out, rows, d, write_x)); \
     else                                                                                                                        \
       RL_LAUNCH_CHECK(rl_launch<false>(normed_add_rmsnorm_kernel<TA, TW, TD, false>, n_rows, th, smem, stream, x,               \
-                                       (const TD*)delta, n_parts, part_stride, (const TW*)wd, eps_d, (const TW*)w, eps,          \
+                                       (const TD*)delta, n_parts, part_stride, bias, (const TW*)wd, eps_d, (const TW*)w, eps,    \
                                        (TA*)out, rows, d, write_x));                                                            \
     return 0;                                                                                                                   \
   } while (0)

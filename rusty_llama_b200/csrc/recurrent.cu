@@ -1,0 +1,241 @@
+// Mixers whose memory is a fixed-size state per sequence instead of a growing cache, and the row kernels around them.
+// The state is 32-bit and lives in the cache's state records, state[slot]; a step reads the record of each of its
+// sequences, runs the sequence's tokens through it in order and writes it back.  Everything that enters a recurrence
+// is computed in 32-bit from the projections, which come in the run's element type.
+//
+//   decay_attn   linear attention with a constant decay per head:
+//                  S_t = decay_h S_(t-1) + k_t v_t^T,  o_t = S_t^T q_t      (S is [dim, vdim] per head)
+//                with an optional activation (silu) applied to the projected q, k, v as they are read.
+//   rms_gate     y = x / sqrt(mean(x^2) + eps) * w * sigmoid(g) * c over whole rows (x 32-bit), the step between
+//                decay_attn and the output projection.
+//   min_gru      element by element  S_t = (1 - z_t) S_(t-1) + z_t c_t,  z = sigmoid(a + b_z),
+//                c = u + 1/2 where u >= 0, else sigmoid(u), u = x + b_x;  result S_t * silu(g_t) * c_out.
+//   unary_act    y = f(x) element by element; f = relu(x)^2.
+#include "common.cuh"
+
+RL_DEFINE_ERROR_TEXT()
+
+__device__ __forceinline__ float logistic(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float silu_f(float x) { return x * logistic(x); }
+
+// ---------------------------------------------------------------- linear attention with decay
+// A block owns 32 columns of one head's state for one sequence: lane = column, warp w holds rows 32 w .. 32 w + 31 of
+// those columns in registers.  Tokens are taken DA_TOK at a time: their q, k (whole head) and v (the block's columns)
+// go to shared memory, every warp runs the tokens through its rows, and the warps' partial results are added in warp
+// order.  The order of every sum is fixed by the sizes alone.
+#define DA_TOK 16
+
+template <typename T>
+__global__ void decay_attn_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int in_stride,
+                                  const float* __restrict__ decay, float* __restrict__ state, const int* __restrict__ slot_ids,
+                                  const int* __restrict__ seq_start, float* __restrict__ out, int out_stride, int H, int dim, int vdim,
+                                  int act) {
+  extern __shared__ float sm[];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * 32;
+  const int col = col0 + lane;
+  const bool col_ok = col < vdim;
+  float* q_s = sm;                      // [DA_TOK][dim]
+  float* k_s = q_s + DA_TOK * dim;      // [DA_TOK][dim]
+  float* v_s = k_s + DA_TOK * dim;      // [DA_TOK][32]
+  float* part = v_s + DA_TOK * 32;      // [nw][DA_TOK][32]
+  const int t0 = seq_start[s], t1 = seq_start[s + 1];
+  const float lam = decay[h];
+  float* st = state + (((size_t)slot_ids[s] * H + h) * dim) * vdim;
+  float S[32];
+#pragma unroll
+  for (int r = 0; r < 32; ++r) {
+    const int row = w * 32 + r;
+    S[r] = (row < dim && col_ok) ? st[(size_t)row * vdim + col] : 0.f;
+  }
+  for (int base = t0; base < t1; base += DA_TOK) {
+    const int n = min(DA_TOK, t1 - base);
+    for (int idx = threadIdx.x; idx < n * dim; idx += blockDim.x) {
+      const int j = idx / dim, i = idx - j * dim;
+      const size_t at = (size_t)(base + j) * in_stride + (size_t)h * dim + i;
+      float qv = to_f32(q[at]), kv = to_f32(k[at]);
+      if (act) {
+        qv = silu_f(qv);
+        kv = silu_f(kv);
+      }
+      q_s[j * dim + i] = qv;
+      k_s[j * dim + i] = kv;
+    }
+    for (int idx = threadIdx.x; idx < n * 32; idx += blockDim.x) {
+      const int j = idx >> 5, c = idx & 31;
+      float vv = 0.f;
+      if (col0 + c < vdim) {
+        vv = to_f32(v[(size_t)(base + j) * in_stride + (size_t)h * vdim + col0 + c]);
+        if (act) vv = silu_f(vv);
+      }
+      v_s[idx] = vv;
+    }
+    __syncthreads();
+    for (int j = 0; j < n; ++j) {
+      const float vj = v_s[j * 32 + lane];
+      const float* kj = k_s + j * dim + w * 32;
+      const float* qj = q_s + j * dim + w * 32;
+      float o = 0.f;
+#pragma unroll
+      for (int r = 0; r < 32; ++r) {
+        if (w * 32 + r < dim) {
+          S[r] = lam * S[r] + kj[r] * vj;
+          o += S[r] * qj[r];
+        }
+      }
+      part[(w * DA_TOK + j) * 32 + lane] = o;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < n * 32; idx += blockDim.x) {
+      const int j = idx >> 5, c = idx & 31;
+      if (col0 + c < vdim) {
+        float o = 0.f;
+        for (int ww = 0; ww < nw; ++ww) o += part[(ww * DA_TOK + j) * 32 + c];
+        out[(size_t)(base + j) * out_stride + (size_t)h * vdim + col0 + c] = o;
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int r = 0; r < 32; ++r) {
+    const int row = w * 32 + r;
+    if (row < dim && col_ok) st[(size_t)row * vdim + col] = S[r];
+  }
+}
+
+RL_API int rl_decay_attn(const void* q, const void* k, const void* v, int dtype, int in_stride, const float* decay, float* state,
+                         const int* slot_ids, const int* seq_start, float* out, int out_stride, int n_seqs, int H, int dim, int vdim,
+                         int act, cudaStream_t stream) {
+  if (n_seqs <= 0 || H <= 0 || dim <= 0 || vdim <= 0) RL_REFUSE(1, "decay_attn: S=%d H=%d dim=%d vdim=%d", n_seqs, H, dim, vdim);
+  if (dim > 1024) RL_REFUSE(2, "decay_attn: key size %d exceeds 1024", dim);
+  if (H > 65535 || (vdim + 31) / 32 > 65535) RL_REFUSE(3, "decay_attn: %d heads or %d columns exceed the grid", H, vdim);
+  const int nw = (dim + 31) / 32;
+  const size_t smem = ((size_t)2 * DA_TOK * dim + DA_TOK * 32 + (size_t)nw * DA_TOK * 32) * sizeof(float);
+  dim3 grid(n_seqs, H, (vdim + 31) / 32);
+#define RL_DA(T)                                                                                                                  \
+  do {                                                                                                                            \
+    if (smem > 48 * 1024) {                                                                                                       \
+      cudaError_t e = cudaFuncSetAttribute(decay_attn_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);          \
+      if (e != cudaSuccess) RL_REFUSE(4, "decay_attn: %zu bytes of shared memory refused", smem);                                 \
+    }                                                                                                                             \
+    decay_attn_kernel<T><<<grid, nw * 32, smem, stream>>>((const T*)q, (const T*)k, (const T*)v, in_stride, decay, state, slot_ids, \
+                                                          seq_start, out, out_stride, H, dim, vdim, act);                         \
+  } while (0)
+  if (dtype == RL_BF16) RL_DA(bf16);
+  else if (dtype == RL_F32) RL_DA(float);
+  else RL_REFUSE(5, "decay_attn: unknown dtype %d", dtype);
+#undef RL_DA
+  RL_LAUNCH_RESULT();
+}
+
+// ---------------------------------------------------------------- norm of a 32-bit row, weight, gate
+template <typename T, typename TW>
+__global__ void rms_gate_kernel(const float* __restrict__ x, int x_stride, const TW* __restrict__ w, float eps, const T* __restrict__ gate,
+                                int gate_stride, float out_scale, T* __restrict__ out, int out_stride, int n) {
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const float* xr = x + (size_t)t * x_stride;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) ss += xr[i] * xr[i];
+  const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)n + eps);
+  const T* g = gate ? gate + (size_t)t * gate_stride : nullptr;
+  T* o = out + (size_t)t * out_stride;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float y = xr[i] * inv * to_f32(w[i]);
+    if (g) y *= logistic(to_f32(g[i]));
+    o[i] = from_f32<T>(y * out_scale);
+  }
+}
+
+RL_API int rl_rms_gate(const float* x, int x_stride, const void* w, int w_dtype, float eps, const void* gate, int gate_stride,
+                       float out_scale, void* out, int out_stride, int act_dtype, int n_rows, int n, cudaStream_t stream) {
+  if (n_rows <= 0 || n <= 0 || !x || !w || !out) RL_REFUSE(1, "rms_gate: rows=%d n=%d", n_rows, n);
+  const int th = n >= 1024 ? 256 : (n >= 256 ? 128 : 64);
+#define RL_RG(T, TW)                                                                                                               \
+  rms_gate_kernel<T, TW><<<n_rows, th, 0, stream>>>(x, x_stride, (const TW*)w, eps, (const T*)gate, gate_stride, out_scale, (T*)out, \
+                                                    out_stride, n)
+  if (act_dtype == RL_BF16 && w_dtype == RL_F32) RL_RG(bf16, float);
+  else if (act_dtype == RL_BF16 && w_dtype == RL_BF16) RL_RG(bf16, bf16);
+  else if (act_dtype == RL_F32 && w_dtype == RL_F32) RL_RG(float, float);
+  else RL_REFUSE(2, "rms_gate: unsupported dtypes act=%d w=%d", act_dtype, w_dtype);
+#undef RL_RG
+  RL_LAUNCH_RESULT();
+}
+
+// ---------------------------------------------------------------- minimal gated recurrent unit
+// One thread per (sequence, channel); the sequence's tokens in order, eight at a time so that their loads are in flight together.
+#define GRU_AHEAD 8
+
+template <typename T>
+__global__ void min_gru_kernel(const T* __restrict__ z, const T* __restrict__ x, const T* __restrict__ g, int in_stride,
+                               const float* __restrict__ z_bias, const float* __restrict__ x_bias, float* __restrict__ state,
+                               const int* __restrict__ slot_ids, const int* __restrict__ seq_start, float out_scale, T* __restrict__ out,
+                               int out_stride, int width) {
+  const int s = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= width) return;
+  const int t0 = seq_start[s], t1 = seq_start[s + 1];
+  float* st = state + (size_t)slot_ids[s] * width + c;
+  float S = *st;
+  const float bz = z_bias ? z_bias[c] : 0.f, bx = x_bias ? x_bias[c] : 0.f;
+  for (int base = t0; base < t1; base += GRU_AHEAD) {
+    float zv[GRU_AHEAD], xv[GRU_AHEAD], gv[GRU_AHEAD];
+#pragma unroll
+    for (int j = 0; j < GRU_AHEAD; ++j) {
+      if (base + j < t1) {
+        const size_t at = (size_t)(base + j) * in_stride + c;
+        zv[j] = to_f32(z[at]);
+        xv[j] = to_f32(x[at]);
+        gv[j] = to_f32(g[at]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < GRU_AHEAD; ++j) {
+      if (base + j < t1) {
+        const float zz = logistic(zv[j] + bz);
+        const float u = xv[j] + bx;
+        const float cand = u >= 0.f ? u + 0.5f : logistic(u);
+        S = (1.0f - zz) * S + zz * cand;
+        out[(size_t)(base + j) * out_stride + c] = from_f32<T>(S * silu_f(gv[j]) * out_scale);
+      }
+    }
+  }
+  *st = S;
+}
+
+RL_API int rl_min_gru(const void* z, const void* x, const void* g, int dtype, int in_stride, const float* z_bias, const float* x_bias,
+                      float* state, const int* slot_ids, const int* seq_start, float out_scale, void* out, int out_stride, int n_seqs,
+                      int width, cudaStream_t stream) {
+  if (n_seqs <= 0 || width <= 0 || !z || !x || !g || !state || !out) RL_REFUSE(1, "min_gru: S=%d width=%d", n_seqs, width);
+  const int th = width >= 128 ? 128 : ((width + 31) / 32) * 32;
+  dim3 grid(n_seqs, (width + th - 1) / th);
+  if (dtype == RL_BF16)
+    min_gru_kernel<bf16><<<grid, th, 0, stream>>>((const bf16*)z, (const bf16*)x, (const bf16*)g, in_stride, z_bias, x_bias, state, slot_ids,
+                                                  seq_start, out_scale, (bf16*)out, out_stride, width);
+  else if (dtype == RL_F32)
+    min_gru_kernel<float><<<grid, th, 0, stream>>>((const float*)z, (const float*)x, (const float*)g, in_stride, z_bias, x_bias, state,
+                                                   slot_ids, seq_start, out_scale, (float*)out, out_stride, width);
+  else
+    RL_REFUSE(2, "min_gru: unknown dtype %d", dtype);
+  RL_LAUNCH_RESULT();
+}
+
+// ---------------------------------------------------------------- element-wise activation
+#define RL_ACT_RELU2 1
+
+template <typename T>
+__global__ void unary_act_kernel(const T* __restrict__ x, T* __restrict__ y, long long total, int kind) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const float v = fmaxf(to_f32(x[i]), 0.f);
+  y[i] = from_f32<T>(v * v);
+}
+
+RL_API int rl_unary_act(const void* x, void* y, int dtype, long long total, int kind, cudaStream_t stream) {
+  if (total <= 0) RL_REFUSE(1, "unary_act: nothing to do");
+  if (kind != RL_ACT_RELU2) RL_REFUSE(2, "unary_act: unknown activation %d", kind);
+  const long long blocks = (total + 255) / 256;
+  if (dtype == RL_BF16) unary_act_kernel<bf16><<<(unsigned)blocks, 256, 0, stream>>>((const bf16*)x, (bf16*)y, total, kind);
+  else if (dtype == RL_F32) unary_act_kernel<float><<<(unsigned)blocks, 256, 0, stream>>>((const float*)x, (float*)y, total, kind);
+  else RL_REFUSE(3, "unary_act: unknown dtype %d", dtype);
+  RL_LAUNCH_RESULT();
+}

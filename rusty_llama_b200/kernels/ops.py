@@ -885,10 +885,11 @@ def sample_chain(
 # ------------------------------------------------------------------ sublayer results that are normed before they are added
 def normed_add_rmsnorm(
     x: torch.Tensor, delta: torch.Tensor, delta_weight: torch.Tensor, delta_eps: float, weight: Optional[torch.Tensor], eps: float,
-    act_dtype: torch.dtype, rows: Optional[torch.Tensor] = None, write_x: bool = True,
+    act_dtype: torch.dtype, rows: Optional[torch.Tensor] = None, write_x: bool = True, delta_bias: Optional[torch.Tensor] = None,
 ) -> Optional[torch.Tensor]:
-    """x (float32 [T, d]) += rmsnorm(sum of delta parts) * delta_weight; returns rmsnorm(x) * weight in `act_dtype`
-    (None without a weight).  delta: [T, d] or [parts, T, d], in `act_dtype` or float32.  Both norm weights have one type."""
+    """x (float32 [T, d]) += rmsnorm(sum of delta parts + delta_bias) * delta_weight; returns rmsnorm(x) * weight in `act_dtype`
+    (None without a weight).  delta: [T, d] or [parts, T, d], in `act_dtype` or float32.  Both norm weights have one type.
+    delta_bias: None or float32 [d], a row that belongs to every row of the summed delta (a projection's bias)."""
     _cuda(x, "normed_add_rmsnorm x", torch.float32)
     T, d = x.shape
     _cuda(delta, "normed_add_rmsnorm delta")
@@ -909,11 +910,14 @@ def normed_add_rmsnorm(
         out = torch.empty((n_rows, d), dtype=act_dtype, device=x.device)
     if rows is not None:
         _cuda(rows, "normed_add_rmsnorm rows", torch.int32)
+    if delta_bias is not None:
+        _cuda(delta_bias, "normed_add_rmsnorm delta_bias", torch.float32)
+        _need(tuple(delta_bias.shape) == (d,) and delta_bias.data_ptr() % 16 == 0, "normed_add_rmsnorm: delta_bias must be an aligned row of d numbers")
     if n_rows == 0:
         return out
     lib = build.load("elementwise")
     rc = lib.rl_normed_add_rmsnorm(
-        _p(x), _p(delta), c_int(_DT[delta.dtype]), c_int(n_parts), c_ll(part_stride), _p(delta_weight), c_float(delta_eps), _p(weight),
+        _p(x), _p(delta), c_int(_DT[delta.dtype]), c_int(n_parts), c_ll(part_stride), _p(delta_bias), _p(delta_weight), c_float(delta_eps), _p(weight),
         c_int(_dt(delta_weight, "normed_add_rmsnorm weight")), c_float(eps), _p(out), c_int(_DT[act_dtype]), _p(rows), c_int(n_rows),
         c_int(d), c_int(1 if write_x else 0), _stream(),
     )
@@ -1219,4 +1223,206 @@ def latent_attn_mma(
         c_int(PAGE_SIZE), c_int(window), c_float(scale), c_int(n_splits), _stream(),
     )
     _check(lib, rc, "latent_attn_mma", kernels=2 if n_splits > 1 else 1)
+    return out
+
+
+# ------------------------------------------------------------------ attention with options (csrc/attention_ext.cu)
+def _check_kv_pages(k_pages, v_pages, dtype, K, kdim, vdim, what):
+    for name, pages, size in (("k_pages", k_pages, kdim), ("v_pages", v_pages, vdim)):
+        _cuda(pages, f"{what} {name}", dtype)
+        _need(
+            pages.dim() == 4 and tuple(pages.shape[1:]) == (K, PAGE_SIZE, size),
+            f"{what}: {name} {tuple(pages.shape)} is not [pages, {K}, {PAGE_SIZE}, {size}]",
+        )
+
+
+def qkv_prep(
+    qkv: torch.Tensor, bias: Optional[torch.Tensor], tok_pos: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor,
+    k_pages: torch.Tensor, v_pages: torch.Tensor, inv_freq: Optional[torch.Tensor], magnitude: float, num_heads: int, num_kv_heads: int,
+    kdim: int, vdim: int, rotary_dim: int, interleaved: bool,
+) -> None:
+    """qkv[T, >= (H + K) kdim + K vdim]: add `bias` (float32, one number per column, or None), rotate the first `rotary_dim`
+    dimensions of every q head (in place) and k head by position * inv_freq, cosines and sines times `magnitude`, and store
+    k and v at each token's place in the paged cache (k_pages [pages, K, PAGE_SIZE, kdim], v_pages [..., vdim])."""
+    _cuda(qkv, "qkv_prep qkv", contiguous=False)
+    stride = _rows(qkv, "qkv_prep qkv")
+    T = qkv.shape[0]
+    cols = (num_heads + num_kv_heads) * kdim + num_kv_heads * vdim
+    _need(qkv.shape[1] >= cols, "qkv_prep: qkv rows too short")
+    _cuda(tok_pos, "qkv_prep tok_pos", torch.int32)
+    _cuda(tok_seq, "qkv_prep tok_seq", torch.int32)
+    _need(tok_pos.numel() == T and tok_seq.numel() == T, "qkv_prep: one position and one sequence index per token")
+    _cuda(block_table, "qkv_prep block_table", torch.int32)
+    _need(block_table.dim() == 2, "qkv_prep: block_table must be [S, width]")
+    _check_kv_pages(k_pages, v_pages, qkv.dtype, num_kv_heads, kdim, vdim, "qkv_prep")
+    if bias is not None:
+        _cuda(bias, "qkv_prep bias", torch.float32)
+        _need(bias.numel() == cols, f"qkv_prep: bias has {bias.numel()} numbers for {cols} columns")
+    if rotary_dim:
+        _cuda(inv_freq, "qkv_prep inv_freq", torch.float32)
+        _need(inv_freq.numel() == rotary_dim // 2, "qkv_prep: inv_freq must hold rotary_dim/2 values")
+    lib = build.load("attention_ext")
+    rc = lib.rl_qkv_prep(
+        _p(qkv), c_int(_dt(qkv, "qkv_prep")), c_int(stride), _p(bias), _p(tok_pos), _p(tok_seq), _p(block_table), c_int(block_table.shape[1]),
+        _p(k_pages), _p(v_pages), _p(inv_freq if rotary_dim else None), c_float(magnitude), c_int(T), c_int(num_heads), c_int(num_kv_heads),
+        c_int(kdim), c_int(vdim), c_int(rotary_dim), c_int(1 if interleaved else 0), c_int(PAGE_SIZE), _stream(),
+    )
+    _check(lib, rc, "qkv_prep")
+
+
+def attn_ext(
+    q: torch.Tensor, k_pages, v_pages, block_table, tok_seq, tok_pos, num_heads: int, num_kv_heads: int, kdim: int, vdim: int,
+    scale: float, window: int = 0, sink: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None,
+    gate: Optional[torch.Tensor] = None, out_scale: float = 1.0, out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Attention of each token over its sequence's cached keys, both element types, prompts and decoding.
+
+    q: [T, >= H kdim] rows.  sink: float32 [H] or None.  mix: float32 [H, H] or None (scores of the heads are mixed before the
+    softmax).  gate: [T, >= H vdim] rows of q's type or None: the result is multiplied by sigmoid(gate).  out: [T, H vdim] rows
+    (a strided view is taken as it is)."""
+    _cuda(q, "attn_ext q", contiguous=False)
+    qs = _rows(q, "attn_ext q")
+    T = q.shape[0]
+    _need(q.shape[1] >= num_heads * kdim, "attn_ext: q rows too short")
+    _check_kv_pages(k_pages, v_pages, q.dtype, num_kv_heads, kdim, vdim, "attn_ext")
+    _cuda(block_table, "attn_ext block_table", torch.int32)
+    _cuda(tok_seq, "attn_ext tok_seq", torch.int32)
+    _cuda(tok_pos, "attn_ext tok_pos", torch.int32)
+    _need(tok_seq.numel() == T and tok_pos.numel() == T and block_table.dim() == 2, "attn_ext: metadata sizes")
+    if sink is not None:
+        _cuda(sink, "attn_ext sink", torch.float32)
+        _need(sink.numel() == num_heads, "attn_ext: one sink per head")
+    if mix is not None:
+        _cuda(mix, "attn_ext mix", torch.float32)
+        _need(tuple(mix.shape) == (num_heads, num_heads), "attn_ext: the mixing matrix must be [H, H]")
+    gs = 0
+    if gate is not None:
+        _cuda(gate, "attn_ext gate", q.dtype, contiguous=False)
+        gs = _rows(gate, "attn_ext gate")
+        _need(gate.shape[0] == T and gate.shape[1] >= num_heads * vdim, "attn_ext: gate rows too short")
+    if out is None:
+        out = torch.empty((T, num_heads * vdim), dtype=q.dtype, device=q.device)
+    _cuda(out, "attn_ext out", q.dtype, contiguous=False)
+    _need(_rows(out, "attn_ext out") >= num_heads * vdim and tuple(out.shape) == (T, num_heads * vdim), "attn_ext: out must be [T, H vdim]")
+    lib = build.load("attention_ext")
+    rc = lib.rl_attn_ext(
+        _p(q), c_int(_dt(q, "attn_ext")), c_int(qs), _p(k_pages), _p(v_pages), _p(block_table), c_int(block_table.shape[1]), _p(tok_seq),
+        _p(tok_pos), _p(sink), _p(mix), _p(gate), c_int(gs), c_float(out_scale), _p(out), c_int(out.stride(0)), c_int(T), c_int(num_heads),
+        c_int(num_kv_heads), c_int(kdim), c_int(vdim), c_int(PAGE_SIZE), c_int(window), c_float(scale), _stream(),
+    )
+    _check(lib, rc, "attn_ext")
+    return out
+
+
+# ------------------------------------------------------------------ recurrent mixers (csrc/recurrent.cu)
+def decay_attn(
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, slot_ids: torch.Tensor,
+    seq_start: torch.Tensor, num_heads: int, dim: int, vdim: int, silu: bool = False, out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Linear attention with a decay per head, S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t, through the sequences' states.
+
+    q, k: [T, H dim], v: [T, H vdim], views of one projection's rows (equal row strides).  decay: float32 [H].
+    state: float32 [slots, H, dim, vdim]; sequence i of the step owns state[slot_ids[i]] and the tokens seq_start[i] .. seq_start[i+1].
+    silu: the activation is applied to q, k and v as they are read.  Returns float32 [T, H vdim]."""
+    for name, t, n in (("q", q, num_heads * dim), ("k", k, num_heads * dim), ("v", v, num_heads * vdim)):
+        _cuda(t, f"decay_attn {name}", q.dtype, contiguous=False)
+        _need(_rows(t, f"decay_attn {name}") == q.stride(0) and t.shape[1] == n and t.shape[0] == q.shape[0], f"decay_attn: {name} has the wrong shape or stride")
+    T = q.shape[0]
+    _cuda(decay, "decay_attn decay", torch.float32)
+    _need(decay.numel() == num_heads, "decay_attn: one decay per head")
+    _cuda(state, "decay_attn state", torch.float32)
+    _need(state.dim() == 4 and tuple(state.shape[1:]) == (num_heads, dim, vdim), f"decay_attn: state {tuple(state.shape)} is not [slots, {num_heads}, {dim}, {vdim}]")
+    _cuda(slot_ids, "decay_attn slot_ids", torch.int32)
+    _cuda(seq_start, "decay_attn seq_start", torch.int32)
+    S = slot_ids.numel()
+    _need(seq_start.numel() == S + 1, "decay_attn: seq_start must hold one more entry than there are sequences")
+    if out is None:
+        out = torch.empty((T, num_heads * vdim), dtype=torch.float32, device=q.device)
+    _cuda(out, "decay_attn out", torch.float32)
+    _need(tuple(out.shape) == (T, num_heads * vdim), "decay_attn: out has the wrong shape")
+    lib = build.load("recurrent")
+    rc = lib.rl_decay_attn(
+        _p(q), _p(k), _p(v), c_int(_dt(q, "decay_attn")), c_int(q.stride(0)), _p(decay), _p(state), _p(slot_ids), _p(seq_start), _p(out),
+        c_int(out.stride(0)), c_int(S), c_int(num_heads), c_int(dim), c_int(vdim), c_int(1 if silu else 0), _stream(),
+    )
+    _check(lib, rc, "decay_attn")
+    return out
+
+
+def rms_gate(
+    x: torch.Tensor, weight: torch.Tensor, eps: float, gate: Optional[torch.Tensor], act_dtype: torch.dtype, out_scale: float = 1.0,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """out = x / sqrt(mean(x^2) + eps) * weight * sigmoid(gate) * out_scale over rows; x float32 [T, n], gate [T, >= n] rows of
+    `act_dtype` or None, out [T, n] rows of `act_dtype` (a strided view is taken as it is)."""
+    _cuda(x, "rms_gate x", torch.float32, contiguous=False)
+    xs = _rows(x, "rms_gate x")
+    T, n = x.shape
+    _cuda(weight, "rms_gate weight")
+    _need(tuple(weight.shape) == (n,), "rms_gate: weight does not match the rows")
+    gs = 0
+    if gate is not None:
+        _cuda(gate, "rms_gate gate", act_dtype, contiguous=False)
+        gs = _rows(gate, "rms_gate gate")
+        _need(gate.shape[0] == T and gate.shape[1] >= n, "rms_gate: gate rows too short")
+    if out is None:
+        out = torch.empty((T, n), dtype=act_dtype, device=x.device)
+    _cuda(out, "rms_gate out", act_dtype, contiguous=False)
+    _need(tuple(out.shape) == (T, n) and _rows(out, "rms_gate out") >= n, "rms_gate: out must be [T, n]")
+    lib = build.load("recurrent")
+    rc = lib.rl_rms_gate(
+        _p(x), c_int(xs), _p(weight), c_int(_dt(weight, "rms_gate weight")), c_float(eps), _p(gate), c_int(gs), c_float(out_scale), _p(out),
+        c_int(out.stride(0)), c_int(_DT[act_dtype]), c_int(T), c_int(n), _stream(),
+    )
+    _check(lib, rc, "rms_gate")
+    return out
+
+
+def min_gru(
+    z: torch.Tensor, x: torch.Tensor, g: torch.Tensor, z_bias: Optional[torch.Tensor], x_bias: Optional[torch.Tensor], state: torch.Tensor,
+    slot_ids: torch.Tensor, seq_start: torch.Tensor, out_scale: float = 1.0, out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Element by element S_t = (1 - z_t) S_(t-1) + z_t c_t with z_t = sigmoid(z + z_bias), u = x + x_bias,
+    c = u + 1/2 where u >= 0 else sigmoid(u); returns S_t * silu(g) * out_scale in the inputs' type.
+
+    z, x, g: [T, width] views of one projection's rows (equal row strides).  state: float32 [slots, width]."""
+    T, width = z.shape
+    for name, t in (("z", z), ("x", x), ("g", g)):
+        _cuda(t, f"min_gru {name}", z.dtype, contiguous=False)
+        _need(_rows(t, f"min_gru {name}") == z.stride(0) and tuple(t.shape) == (T, width), f"min_gru: {name} has the wrong shape or stride")
+    for name, b in (("z_bias", z_bias), ("x_bias", x_bias)):
+        if b is not None:
+            _cuda(b, f"min_gru {name}", torch.float32)
+            _need(b.numel() == width, f"min_gru: {name} does not match the width")
+    _cuda(state, "min_gru state", torch.float32)
+    _need(state.dim() == 2 and state.shape[1] == width, f"min_gru: state {tuple(state.shape)} is not [slots, {width}]")
+    _cuda(slot_ids, "min_gru slot_ids", torch.int32)
+    _cuda(seq_start, "min_gru seq_start", torch.int32)
+    S = slot_ids.numel()
+    _need(seq_start.numel() == S + 1, "min_gru: seq_start must hold one more entry than there are sequences")
+    if out is None:
+        out = torch.empty((T, width), dtype=z.dtype, device=z.device)
+    _cuda(out, "min_gru out", z.dtype, contiguous=False)
+    _need(tuple(out.shape) == (T, width) and _rows(out, "min_gru out") >= width, "min_gru: out must be [T, width]")
+    lib = build.load("recurrent")
+    rc = lib.rl_min_gru(
+        _p(z), _p(x), _p(g), c_int(_dt(z, "min_gru")), c_int(z.stride(0)), _p(z_bias), _p(x_bias), _p(state), _p(slot_ids), _p(seq_start),
+        c_float(out_scale), _p(out), c_int(out.stride(0)), c_int(S), c_int(width), _stream(),
+    )
+    _check(lib, rc, "min_gru")
+    return out
+
+
+ACT_RELU2 = 1  # relu(x)^2
+
+
+def unary_act(x: torch.Tensor, kind: int = ACT_RELU2) -> torch.Tensor:
+    """y = f(x) element by element in 32-bit, stored in x's type."""
+    _cuda(x, "unary_act x")
+    out = torch.empty_like(x)
+    if x.numel() == 0:
+        return out
+    lib = build.load("recurrent")
+    rc = lib.rl_unary_act(_p(x), _p(out), c_int(_dt(x, "unary_act")), c_ll(x.numel()), c_int(kind), _stream())
+    _check(lib, rc, "unary_act")
     return out

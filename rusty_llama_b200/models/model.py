@@ -87,10 +87,11 @@ class Model:
         from ..parts.base import KVNeed
 
         total = 0
-        for _, need in self.cache_needs():
-            if isinstance(need, KVNeed):
-                size = torch.empty((), dtype=need.dtype or self.rt.dtype).element_size()
-                total += (2 if need.values else 1) * need.num_kv_heads * need.head_dim * size
+        for _, needs in self.cache_needs():
+            for need in needs if isinstance(needs, (tuple, list)) else (needs,):
+                if isinstance(need, KVNeed):
+                    size = torch.empty((), dtype=need.dtype or self.rt.dtype).element_size()
+                    total += need.num_kv_heads * (need.head_dim + ((need.value_dim or need.head_dim) if need.values else 0)) * size
         return total
 
     def new_cache(self, max_tokens: int, max_seqs: int) -> Cache:
@@ -103,7 +104,7 @@ class Model:
         for run, entry in enumerate(self.spec.schedule):
             block = self.blocks[entry.layer]
             source = run if entry.cache_from is None else entry.cache_from
-            view = cache.view(source, tables) if source in cache._where else None
+            view = cache.view(source, tables) if cache.owns(source) else None
             block.forward(stream, step, view, shared_cache=entry.cache_from is not None)
         if step.rows is None or step.rows.numel() == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.rt.device)

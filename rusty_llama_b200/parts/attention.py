@@ -41,19 +41,36 @@ def decode_splits(n_seqs: int, num_heads: int, num_kv_heads: int, kv_len: int, h
     return max(1, min(want, tiles, 64))
 
 
+_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight", "gate": "g", "sink": "sink", "head_mix": "talk",
+          "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias", "o_bias": "o_proj.bias"}
+
+
 @MIXERS.register("attention")
 class Attention(Mixer):
     """q = Wq xn, k = Wk xn, v = Wv xn; positions encoded into q and k; k, v stored in the
     cache; each query attends to its sequence's keys up to its own position (all of
     them, or the last `window`); the heads' results go through Wo
     (src/model.rs:1253-1301, src/backend/cpu.rs:363-433).  Query head h reads kv head
-    h // (H / K); the score scale is 1/sqrt(head_dim).
+    h // (H / K); the score scale is 1/sqrt(head_dim) unless `scale` names another.
 
     params: hidden_size, num_heads, num_kv_heads, head_dim, window (0 = all keys),
             position (a PartSpec of the position family).
-    tensors: <prefix>q_proj.weight [H hd, d], k_proj.weight [K hd, d], v_proj.weight [K hd, d],
-             o_proj.weight [d, H hd].  q, k, v are kept as one matrix so that one product
-             serves the three (src/backend/cuda.rs:423-442)."""
+    Optional params, each absent from a plain attention: value_dim (the size of a value head where it differs
+    from head_dim), scale, sink (bool: exp(sink_h) joins the softmax's denominator), head_mix (bool: the heads' scaled
+    scores are mixed by a learned [H, H] matrix before the softmax), gate (bool: the concatenated heads are multiplied
+    by sigmoid(Wg xn) before Wo), bias (bool: q, k, v and the output projection have biases), out_scale (a constant
+    factor on the result, applied in 32-bit where the heads' result is formed), names (tensor names after the prefix,
+    keys q k v o gate sink head_mix q_bias k_bias v_bias o_bias).
+    tensors: <prefix>q_proj.weight [H hd, d], k_proj.weight [K hd, d], v_proj.weight [K vd, d],
+             o_proj.weight [d, H vd]; with the options also g [H vd, d], sink [H], talk [H, H] and the biases.
+             q, k, v (and the gate) are kept as one matrix so that one product
+             serves them all (src/backend/cuda.rs:423-442).
+
+    A plain attention runs on the kernels built for it (tensor-core prompt attention, TMA-fed decode attention, the rotation
+    fused with the cache write or with the decode kernel).  With any of the options it runs on `qkv_prep` and `attn_ext`
+    (csrc/attention_ext.cu), which take every option and both element types."""
+
+    takes_out = True
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -62,50 +79,118 @@ class Attention(Mixer):
         self.K = int(self._param("num_kv_heads"))
         self.hd = int(self._param("head_dim"))
         self.window = int(self._param("window"))
-        if self.H % self.K:
+        self.vd = int(spec.params.get("value_dim") or self.hd)
+        self.has_sink = bool(spec.params.get("sink", False))
+        self.has_mix = bool(spec.params.get("head_mix", False))
+        self.has_gate = bool(spec.params.get("gate", False))
+        self.has_bias = bool(spec.params.get("bias", False))
+        self.out_scale = float(spec.params.get("out_scale", 1.0))
+        self.names = dict(_NAMES, **dict(spec.params.get("names", {})))
+        if min(self.H, self.K, self.hd, self.vd) <= 0 or self.H % self.K:
             raise ConfigError(f"attention: {self.H} heads are not a multiple of {self.K} kv heads")
-        if self.hd > 256:
-            raise ConfigError(f"attention: head_dim {self.hd} is above 256, the most the attention kernels built here take")
-        if self.hd % 8 and runtime.dtype != torch.float32:
-            raise ConfigError(
-                f"attention: the bfloat16 kernels move a head in 16-byte pieces and need head_dim to be a multiple of 8, got {self.hd} "
-                f"(a float32 run takes any head size up to 256)")
         pos_spec = self._param("position")
         if not isinstance(pos_spec, PartSpec):
             raise ConfigError("attention: 'position' must be a PartSpec")
         self.position = POSITIONS.build(pos_spec, runtime)
-        self.scale = 1.0 / math.sqrt(self.hd)
-        self.qd, self.kvd = self.H * self.hd, self.K * self.hd
+        magnitude = float(getattr(self.position, "magnitude", 1.0))
+        self.extended = (self.vd != self.hd or self.has_sink or self.has_mix or self.has_gate or self.has_bias
+                         or self.out_scale != 1.0 or magnitude != 1.0)
+        if self.extended:
+            if max(self.hd, self.vd) > 256:
+                raise ConfigError(f"attention: head sizes {self.hd} / {self.vd} are above 256, the most the attention kernels built here take")
+            if self.has_mix and self.H > 32:
+                raise ConfigError(f"attention: the scores of {self.H} heads cannot be mixed, the kernel built here takes 32")
+            rotary_dim = int(getattr(self.position, "rotary_dim", 0))
+            if rotary_dim and not hasattr(self.position, "inv_freq"):
+                raise ConfigError("attention: with its options the mixer rotates by a frequency table itself and needs a 'rotary' position part (or none)")
+            self.rotation = (getattr(self.position, "inv_freq", None), rotary_dim, bool(getattr(self.position, "interleaved", False)), magnitude)
+        else:
+            if self.hd > 256:
+                raise ConfigError(f"attention: head_dim {self.hd} is above 256, the most the attention kernels built here take")
+            if self.hd % 8 and runtime.dtype != torch.float32:
+                raise ConfigError(
+                    f"attention: the bfloat16 kernels move a head in 16-byte pieces and need head_dim to be a multiple of 8, got {self.hd} "
+                    f"(a float32 run takes any head size up to 256)")
+        self.scale = float(spec.params.get("scale") or 1.0 / math.sqrt(self.hd))
+        self.qd, self.kvd, self.vvd, self.od = self.H * self.hd, self.K * self.hd, self.K * self.vd, self.H * self.vd
         self.w_qkv = None
         self.w_o = None
+        self.b_in = self.b_o = self.sink = self.mix = None
 
     def cache_need(self):
-        return KVNeed(self.K, self.hd, self.window)
+        return KVNeed(self.K, self.hd, self.window, value_dim=self.vd if self.vd != self.hd else None)
 
     def children(self):
         return (self.position,)
 
     def param_infos(self) -> Dict[str, ParamInfo]:
-        p = self.prefix
-        return {
-            p + "q_proj.weight": ParamInfo((self.qd, self.d)),
-            p + "k_proj.weight": ParamInfo((self.kvd, self.d)),
-            p + "v_proj.weight": ParamInfo((self.kvd, self.d)),
-            p + "o_proj.weight": ParamInfo((self.d, self.qd)),
+        p, n = self.prefix, self.names
+        infos = {
+            p + n["q"]: ParamInfo((self.qd, self.d)),
+            p + n["k"]: ParamInfo((self.kvd, self.d)),
+            p + n["v"]: ParamInfo((self.vvd, self.d)),
+            p + n["o"]: ParamInfo((self.d, self.od)),
         }
+        if self.has_gate:
+            infos[p + n["gate"]] = ParamInfo((self.od, self.d))
+        if self.has_sink:
+            infos[p + n["sink"]] = ParamInfo((self.H,), "scalars")
+        if self.has_mix:
+            infos[p + n["head_mix"]] = ParamInfo((self.H, self.H), "scalars")
+        if self.has_bias:
+            for key, size in (("q_bias", self.qd), ("k_bias", self.kvd), ("v_bias", self.vvd), ("o_bias", self.d)):
+                infos[p + n[key]] = ParamInfo((size,), "scalars", centre=0.0)
+        return infos
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
-        p = self.prefix
-        self.w_qkv = torch.cat(
-            [tensors[p + "q_proj.weight"], tensors[p + "k_proj.weight"], tensors[p + "v_proj.weight"]], dim=0
-        ).contiguous()
-        self.w_o = tensors[p + "o_proj.weight"].contiguous()
+        p, n = self.prefix, self.names
+        parts = [tensors[p + n["q"]], tensors[p + n["k"]], tensors[p + n["v"]]]
+        if self.has_gate:
+            parts.append(tensors[p + n["gate"]])
+        self.w_qkv = torch.cat(parts, dim=0).contiguous()
+        self.w_o = tensors[p + n["o"]].contiguous()
+        if self.has_sink:
+            self.sink = tensors[p + n["sink"]].contiguous()
+        if self.has_mix:
+            self.mix = tensors[p + n["head_mix"]].contiguous()
+        if self.has_bias:
+            self.b_in = torch.cat([tensors[p + n["q_bias"]], tensors[p + n["k_bias"]], tensors[p + n["v_bias"]]]).contiguous()
+            self.b_o = (tensors[p + n["o_bias"]] * self.out_scale).contiguous()
+
+    def output_bias(self):
+        return self.b_o
 
     def forward(self, xn: torch.Tensor, step, cache, shared_cache: bool = False) -> torch.Tensor:
         a, w_o = self.forward_unprojected(xn, step, cache, shared_cache)
         return linear_to_stream(a, w_o)
 
-    def forward_unprojected(self, xn: torch.Tensor, step, cache, shared_cache: bool = False):
+    def _forward_extended(self, xn: torch.Tensor, step, cache, shared_cache: bool, out):
+        if shared_cache:
+            raise ConfigError("attention: a layer that reads another layer's cache cannot have this mixer's options")
+        proj = linear(xn, self.w_qkv)
+        inv_freq, rotary_dim, interleaved, magnitude = self.rotation
+        ops.qkv_prep(
+            proj, self.b_in, step.tok_pos, step.tok_seq, cache.block_table, cache.k_pages, cache.v_pages, inv_freq, magnitude,
+            self.H, self.K, self.hd, self.vd, rotary_dim, interleaved,
+        )
+        gate = proj[:, self.qd + self.kvd + self.vvd :] if self.has_gate else None
+        a = ops.attn_ext(
+            proj, cache.k_pages, cache.v_pages, cache.block_table, step.tok_seq, step.tok_pos, self.H, self.K, self.hd, self.vd,
+            self.scale, window=self.window, sink=self.sink, mix=self.mix, gate=gate, out_scale=self.out_scale, out=out,
+        )
+        return a, self.w_o
+
+    def forward_unprojected(self, xn: torch.Tensor, step, cache, shared_cache: bool = False, out=None):
+        """out: None, or a [T, H value_dim] view (dense rows, any row stride) that receives the heads' result."""
+        if self.extended:
+            return self._forward_extended(xn, step, cache, shared_cache, out)
+        a, w_o = self._forward_plain(xn, step, cache, shared_cache)
+        if out is not None:
+            out.copy_(a)
+            a = out
+        return a, w_o
+
+    def _forward_plain(self, xn: torch.Tensor, step, cache, shared_cache: bool = False):
         # a decode step of a bfloat16 run at head size 64 or 128: the attention kernel turns the queries and the
         # new key and stores key and value itself, if the position encoding is one it knows how to apply
         fusion = None

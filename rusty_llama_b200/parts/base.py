@@ -91,10 +91,14 @@ class ParamInfo:
     32-bit path).  kind "vector": a tensor stored in 32-bit stays so; otherwise
     it follows the run.  kind "scalars": a few learned numbers that enter 32-bit
     arithmetic directly (a softmax sink, a router's bias, a router's rows): always
-    float32 at run time.  kind "table": integers, kept as int32."""
+    float32 at run time.  kind "table": integers, kept as int32.
+
+    centre: what random weights of a "vector" are drawn around when a model is made from a seed (None: 1, the
+    neutral value of a norm's weight; a norm that stores its weight's distance from one names 0)."""
 
     shape: Tuple[int, ...]
     kind: str = "matrix"
+    centre: Optional[float] = None
 
 
 def runtime_dtype(info: ParamInfo, stored: torch.dtype, run: torch.dtype) -> torch.dtype:
@@ -113,13 +117,15 @@ class KVNeed:
     """Keys and values of every position (window 0) or of the last `window` positions.
 
     values=False: the mixer keeps one row per position and head only (a latent from which it
-    makes keys and values itself); the group then has no value pages."""
+    makes keys and values itself); the group then has no value pages.
+    value_dim: the size of a value row where it differs from a key row's `head_dim` (None: the same)."""
 
     num_kv_heads: int
     head_dim: int
     window: int = 0
     dtype: Optional[torch.dtype] = None  # None: the run's activation type
     values: bool = True
+    value_dim: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -167,16 +173,20 @@ class ResidualStream:
         self.x = x
         self.act_dtype = act_dtype
         self.pending: Optional[torch.Tensor] = None
-        # (weight, eps) of an RMSNorm that what is pending goes through before it is added (a layer that
+        # (weight, eps, bias) of an RMSNorm that what is pending goes through before it is added (a layer that
         # norms its sublayers' results); None: it is added as it is
         self.pending_norm = None
 
-    def add(self, delta: torch.Tensor, norm=None) -> None:
-        """norm: None, or (weight, eps): the stream receives rmsnorm(delta) * weight instead of delta."""
+    def add(self, delta: torch.Tensor, norm=None, bias: Optional[torch.Tensor] = None) -> None:
+        """norm: None, or (weight, eps): the stream receives rmsnorm(delta) * weight instead of delta.
+        bias: None, or a float32 row [d] that belongs to every row of delta (the bias of the projection that made it); the
+        kernel that norms delta adds it first, so it needs a norm."""
         if self.pending is not None:
             self.flush()
+        if bias is not None and norm is None:
+            raise ConfigError("a sublayer's result with a bias row can only be added through a norm of that result")
         self.pending = delta
-        self.pending_norm = norm
+        self.pending_norm = None if norm is None else (norm[0], norm[1], bias)
 
     def take_pending(self):
         """(delta, norm) of what is pending, which is the caller's to add from now on."""
@@ -189,7 +199,8 @@ class ResidualStream:
 
         if self.pending is not None:
             if self.pending_norm is not None:
-                ops.normed_add_rmsnorm(self.x, self.pending, self.pending_norm[0], self.pending_norm[1], None, 0.0, self.act_dtype)
+                ops.normed_add_rmsnorm(self.x, self.pending, self.pending_norm[0], self.pending_norm[1], None, 0.0, self.act_dtype,
+                                       delta_bias=self.pending_norm[2])
             else:
                 ops.add_rmsnorm(self.x, self.pending, None, 0.0, self.act_dtype)
             self.pending = self.pending_norm = None
@@ -240,7 +251,13 @@ class PositionEncoding(Part):
 
 class Mixer(Part):
     def cache_need(self):
-        """KVNeed, StateNeed or None."""
+        """KVNeed, StateNeed, None, or a tuple of needs (a mixer made of several): `forward` then gets a tuple of views
+        in the same order."""
+        return None
+
+    def output_bias(self) -> Optional[torch.Tensor]:
+        """None, or a float32 row [d] that belongs to every row of what `forward` returns (the bias of a last projection,
+        left to the kernel that takes the result next)."""
         return None
 
     def forward(self, xn: torch.Tensor, step, cache, shared_cache: bool = False) -> torch.Tensor:

@@ -72,3 +72,34 @@ class GatedMLP(FeedForward):
         else:
             h = ops.swiglu(linear(xn, self.w_gate_up))
         return linear_to_stream(h, self.w_down)
+
+
+@FEED_FORWARDS.register("mlp")
+class MLP(FeedForward):
+    """f = W_down act(W_up x), no gate.  act "relu2": the square of relu, applied in 32-bit to the up product's values.
+
+    params: hidden_size, intermediate_size, activation ("relu2"), names (optional: keys up down).
+    tensors: <prefix>up_proj.weight [ff, d], down_proj.weight [d, ff]."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.d = int(self._param("hidden_size"))
+        self.ff = int(self._param("intermediate_size"))
+        self.activation = self._param("activation")
+        if self.activation != "relu2":
+            raise ConfigError(f"mlp: activation '{self.activation}' is not built (only 'relu2')")
+        self.names = dict({"up": "up_proj.weight", "down": "down_proj.weight"}, **dict(spec.params.get("names", {})))
+        self.w_up = self.w_down = None
+
+    def param_infos(self) -> Dict[str, ParamInfo]:
+        p = self.prefix
+        return {p + self.names["up"]: ParamInfo((self.ff, self.d)), p + self.names["down"]: ParamInfo((self.d, self.ff))}
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        p = self.prefix
+        self.w_up = tensors[p + self.names["up"]].contiguous()
+        self.w_down = tensors[p + self.names["down"]].contiguous()
+
+    def forward(self, xn: torch.Tensor, step) -> torch.Tensor:
+        h = ops.unary_act(linear(xn, self.w_up), ops.ACT_RELU2)
+        return linear_to_stream(h, self.w_down)

@@ -33,7 +33,10 @@ def _tensor_seed(seed: int, name: str) -> int:
 def random_tensor(name: str, info: ParamInfo, seed: int, dtype: torch.dtype, std: float, norm_jitter: float, device="cpu") -> torch.Tensor:
     gen = torch.Generator(device=device)
     gen.manual_seed(_tensor_seed(seed, name))
-    if info.kind == "vector":
+    if info.centre is not None and info.kind in ("vector", "scalars"):
+        # a tensor that says what its values lie around (a norm's distance from one, a bias): spread by the jitter, or a tenth
+        t = info.centre + (norm_jitter or 0.1) * torch.randn(info.shape, generator=gen, dtype=torch.float32, device=device)
+    elif info.kind == "vector":
         t = torch.ones(info.shape, dtype=torch.float32, device=device)
         if norm_jitter:
             t += norm_jitter * torch.randn(info.shape, generator=gen, dtype=torch.float32, device=device)
