@@ -90,7 +90,7 @@ attn_decode_split_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
                          const bf16* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
                          const int* __restrict__ seq_len, float* __restrict__ part_o,
                          float* __restrict__ part_ml, int H, int K, int hd, int window, float scale_log2,
-                         int n_splits) {
+                         int n_splits, const float* __restrict__ sink) {
   constexpr int STRIDE = HD + 8;  // 16 bytes of padding per row keep ldmatrix free of bank conflicts
   constexpr int KSTEPS = HD / 16;
   constexpr int DTILES = HD / 16;
@@ -115,6 +115,17 @@ attn_decode_split_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
   for (int i = 0; i < DTILES; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY};  // heads 2*t4, 2*t4+1
   float l_run[2] = {0.f, 0.f};              // per-thread partial sums over this thread's keys
+  if (sink != nullptr && split == 0) {
+    // a key without a value whose score is sink[head]: the first part of the key range starts its maximum there and
+    // counts it once in its sum (a learned number that no kernel writes: read before the dependency wait)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      if (2 * t4 + j < n_heads) {
+        m_run[j] = sink[h0 + 2 * t4 + j] * 1.4426950408889634f;
+        l_run[j] = (g == 0) ? 1.f : 0.f;
+      }
+    }
+  }
 
   // (no explicit trigger: the next kernel is released when this one's blocks have finished)
   // zero the padding (columns past hd, rows past the group's heads) once; this needs nothing from
@@ -288,7 +299,7 @@ template <int HD, int STAGES>
 static int launch_decode_stages(const bf16* q, int q_stride, const bf16* k_pages, const bf16* v_pages,
                          const int* block_table, int table_width, const int* seq_len, float* part_o,
                          float* part_ml, bf16* out, int out_stride, int n_seqs, int H, int K, int hd, int window,
-                         float scale, int n_splits, cudaStream_t stream) {
+                         float scale, int n_splits, const float* sink, cudaStream_t stream) {
   const size_t smem = (size_t)(HEADS + 2 * STAGES * BK) * (HD + 8) * sizeof(bf16);
   auto kern = attn_decode_split_kernel<HD, STAGES>;
   if (smem > 48 * 1024) {
@@ -298,7 +309,7 @@ static int launch_decode_stages(const bf16* q, int q_stride, const bf16* k_pages
   const int G = H / K;
   dim3 grid(n_splits, K * ((G + HEADS - 1) / HEADS), n_seqs);
   RL_LAUNCH_CHECK(rl_launch(kern, grid, 32, smem, stream, q, q_stride, k_pages, v_pages, block_table, table_width, seq_len,
-                            part_o, part_ml, H, K, hd, window, scale * 1.4426950408889634f, n_splits));
+                            part_o, part_ml, H, K, hd, window, scale * 1.4426950408889634f, n_splits, sink));
   dim3 grid2(H, n_seqs);
   RL_LAUNCH_CHECK(rl_launch(attn_decode_merge_kernel, grid2, 128, 0, stream, (const float*)part_o, (const float*)part_ml,
                             out, out_stride, H, hd, n_splits));
@@ -309,7 +320,7 @@ template <int HD>
 static int launch_decode(const bf16* q, int q_stride, const bf16* k_pages, const bf16* v_pages,
                          const int* block_table, int table_width, const int* seq_len, float* part_o,
                          float* part_ml, bf16* out, int out_stride, int n_seqs, int H, int K, int hd, int window,
-                         float scale, int n_splits, cudaStream_t stream) {
+                         float scale, int n_splits, const float* sink, cudaStream_t stream) {
   // Three stages (measured best at batch 8 and 64 once the splits are chosen to fill the GPU once);
   // RL_ATTN_STAGES=2 in the environment selects two, for measurements.
   static int forced = -1;
@@ -320,17 +331,18 @@ static int launch_decode(const bf16* q, int q_stride, const bf16* k_pages, const
   const int stages = forced == 2 ? 2 : 3;
   if (stages == 2)
     return launch_decode_stages<HD, 2>(q, q_stride, k_pages, v_pages, block_table, table_width, seq_len, part_o, part_ml,
-                                       out, out_stride, n_seqs, H, K, hd, window, scale, n_splits, stream);
+                                       out, out_stride, n_seqs, H, K, hd, window, scale, n_splits, sink, stream);
   return launch_decode_stages<HD, 3>(q, q_stride, k_pages, v_pages, block_table, table_width, seq_len, part_o, part_ml,
-                                     out, out_stride, n_seqs, H, K, hd, window, scale, n_splits, stream);
+                                     out, out_stride, n_seqs, H, K, hd, window, scale, n_splits, sink, stream);
 }
 
 // Scratch needed, in floats: n_seqs * H * n_splits * (hd + 2); the caller passes part_o of
 // n_seqs*H*n_splits*hd floats and part_ml of n_seqs*H*n_splits*2.
-RL_API int rl_attn_decode(const void* q, int dtype, int q_stride, const void* k_pages, const void* v_pages,
-                          const int* block_table, int table_width, const int* seq_len, float* part_o,
-                          float* part_ml, void* out, int out_stride, int n_seqs, int H, int K, int hd,
-                          int page_size, int window, float scale, int n_splits, cudaStream_t stream) {
+// sink: nullptr, or one learned score per head that joins the softmax's denominator and nothing else.
+RL_API int rl_attn_decode_sink(const void* q, int dtype, int q_stride, const void* k_pages, const void* v_pages,
+                               const int* block_table, int table_width, const int* seq_len, float* part_o,
+                               float* part_ml, void* out, int out_stride, int n_seqs, int H, int K, int hd,
+                               int page_size, int window, float scale, int n_splits, const float* sink, cudaStream_t stream) {
   if (n_seqs <= 0 || H <= 0 || K <= 0 || hd <= 0) RL_REFUSE(1, "attn_decode: S=%d H=%d K=%d hd=%d", n_seqs, H, K, hd);
   if (H % K) RL_REFUSE(2, "attn_decode: %d query heads are not a multiple of %d kv heads", H, K);
   if (page_size != PAGE) RL_REFUSE(3, "attn_decode: page size %d, this kernel is built for %d", page_size, PAGE);
@@ -345,13 +357,21 @@ RL_API int rl_attn_decode(const void* q, int dtype, int q_stride, const void* k_
   bf16* oo = (bf16*)out;
 #define RL_DECODE(HDV)                                                                                              \
   return launch_decode<HDV>(qq, q_stride, kp, vp, block_table, table_width, seq_len, part_o, part_ml, oo, out_stride, \
-                            n_seqs, H, K, hd, window, scale, n_splits, stream)
+                            n_seqs, H, K, hd, window, scale, n_splits, sink, stream)
   if (hd <= 32) RL_DECODE(32);
   if (hd <= 64) RL_DECODE(64);
   if (hd <= 128) RL_DECODE(128);
   if (hd <= 256) RL_DECODE(256);
 #undef RL_DECODE
   RL_REFUSE(10, "attn_decode: head size %d exceeds 256", hd);
+}
+
+RL_API int rl_attn_decode(const void* q, int dtype, int q_stride, const void* k_pages, const void* v_pages,
+                          const int* block_table, int table_width, const int* seq_len, float* part_o,
+                          float* part_ml, void* out, int out_stride, int n_seqs, int H, int K, int hd,
+                          int page_size, int window, float scale, int n_splits, cudaStream_t stream) {
+  return rl_attn_decode_sink(q, dtype, q_stride, k_pages, v_pages, block_table, table_width, seq_len, part_o, part_ml, out, out_stride,
+                             n_seqs, H, K, hd, page_size, window, scale, n_splits, nullptr, stream);
 }
 
 // ------------------------------------------------------------------ the same, with built-in scratch

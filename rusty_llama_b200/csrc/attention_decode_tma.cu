@@ -100,7 +100,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                        const float* __restrict__ inv_freq, int rot, int interleaved,
                        unsigned int* __restrict__ counters, bf16* __restrict__ out, int out_stride,
                        const float* __restrict__ q_parts, int n_parts, long long part_stride, int test_role,
-                       uint32_t test_ns) {
+                       uint32_t test_ns, const float* __restrict__ sink) {
   // all shared memory is dynamic, so that the ring starts at the block's first byte (1024-byte
   // aligned, as the 128-byte swizzle needs)
   constexpr int STAGES = Shape<HD>::STAGES, STAGE_BYTES = Shape<HD>::STAGE_BYTES, BOXES = Shape<HD>::BOXES;
@@ -259,6 +259,17 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   for (int i = 0; i < HD / 16; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY};  // heads 2*t4, 2*t4+1
   float l_run[2] = {0.f, 0.f};              // per-thread partial sums over this thread's keys
+  if (sink != nullptr && split == 0 && warp == 0) {
+    // a key without a value whose score is sink[head]: one warp of the first part of the key range starts its maximum
+    // there and counts it once in its sum
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      if (2 * t4 + j < n_heads) {
+        m_run[j] = sink[h0 + 2 * t4 + j] * 1.4426950408889634f;
+        l_run[j] = (g == 0) ? 1.f : 0.f;
+      }
+    }
+  }
 
   // rows this lane addresses in the ldmatrix calls: K as A operand (16 keys x 16 dims), V transposed
   const int k_row = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), k_piece = lane >> 4;      // + 2 * kk
@@ -572,7 +583,7 @@ static int launch_decode_tma(const void* q, int q_stride, const void* k_pages, c
                              void* out, int out_stride, int n_seqs, int H, int K, int window, float scale, int n_splits,
                              int* status, int fuse, const float* inv_freq, int rot, int interleaved, unsigned int* counters,
                              const float* q_parts, int n_parts, long long part_stride, int wait_test_role,
-                             unsigned int wait_test_ns, cudaStream_t stream) {
+                             unsigned int wait_test_ns, const float* sink, cudaStream_t stream) {
   CUtensorMap map_k, map_v;
   if (make_page_map(&map_k, k_pages, n_pages, K, PAGE, HD, PAGE) || make_page_map(&map_v, v_pages, n_pages, K, PAGE, HD, PAGE))
     RL_REFUSE(10, "attn_decode_tma: cannot describe the cache pages to TMA");
@@ -586,7 +597,7 @@ static int launch_decode_tma(const void* q, int q_stride, const void* k_pages, c
                             table_width, seq_len, part_o, part_ml, H, K, window, scale * 1.4426950408889634f, n_splits, status,
                             fuse, (bf16*)const_cast<void*>(k_pages), (bf16*)const_cast<void*>(v_pages), inv_freq, fuse ? rot : 0,
                             interleaved, counters, (bf16*)out, out_stride, q_parts, n_parts, part_stride, wait_test_role,
-                            (uint32_t)wait_test_ns));
+                            (uint32_t)wait_test_ns, sink));
   if (counters != nullptr) return 0;
   dim3 grid2(H, n_seqs);
   RL_LAUNCH_CHECK(rl_launch(attn_decode_merge_kernel, grid2, 128, 0, stream, (const float*)part_o, (const float*)part_ml,
@@ -599,7 +610,8 @@ RL_API int rl_attn_decode_tma(const void* q, int q_stride, const void* k_pages, 
                               void* out, int out_stride, int n_seqs, int H, int K, int hd, int page_size, int window,
                               float scale, int n_splits, int* status, int fuse, const float* inv_freq, int rot,
                               int interleaved, unsigned int* counters, const float* q_parts, int n_parts,
-                              long long part_stride, int wait_test_role, unsigned int wait_test_ns, cudaStream_t stream) {
+                              long long part_stride, int wait_test_role, unsigned int wait_test_ns, const float* sink,
+                              cudaStream_t stream) {
   if (n_seqs <= 0 || H <= 0 || K <= 0 || n_pages <= 0) RL_REFUSE(1, "attn_decode_tma: S=%d H=%d K=%d pages=%d", n_seqs, H, K, n_pages);
   if (!rl_attn_decode_tma_takes(hd)) RL_REFUSE(2, "attn_decode_tma: head size %d, this kernel is built for 64 and 128", hd);
   if (H % K) RL_REFUSE(3, "attn_decode_tma: %d query heads are not a multiple of %d kv heads", H, K);
@@ -616,7 +628,7 @@ RL_API int rl_attn_decode_tma(const void* q, int q_stride, const void* k_pages, 
 #define RL_DECODE_TMA(HDV)                                                                                                  \
   return launch_decode_tma<HDV>(q, q_stride, k_pages, v_pages, n_pages, block_table, table_width, seq_len, part_o, part_ml, out, \
                                 out_stride, n_seqs, H, K, window, scale, n_splits, status, fuse, inv_freq, rot, interleaved,      \
-                                counters, q_parts, n_parts, part_stride, wait_test_role, wait_test_ns, stream)
+                                counters, q_parts, n_parts, part_stride, wait_test_role, wait_test_ns, sink, stream)
   if (hd == 64) RL_DECODE_TMA(64);
   RL_DECODE_TMA(128);
 #undef RL_DECODE_TMA

@@ -70,7 +70,7 @@ flash_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __res
                      const bf16* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
                      const int* __restrict__ seq_start, const int* __restrict__ seq_pos0,
                      bf16* __restrict__ out, int out_stride, int H, int K, int hd, int window,
-                     float scale_log2) {
+                     float scale_log2, const float* __restrict__ sink) {
   constexpr int STRIDE = HD + 8;  // 16 bytes of padding per row keeps ldmatrix free of bank conflicts
   constexpr int KSTEPS = HD / 16;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -128,6 +128,10 @@ flash_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __res
   for (int i = 0; i < HD / 8; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY};
   float l_run[2] = {0.f, 0.f};  // per-thread partial sums, reduced over the quad at the end
+  if (sink != nullptr) {  // a key without a value whose score is sink[h]: it starts the maximum and counts once in the sum
+    m_run[0] = m_run[1] = sink[h] * 1.4426950408889634f;
+    l_run[0] = l_run[1] = (t4 == 0) ? 1.f : 0.f;
+  }
   const int qpos[2] = {first_pos + warp * 16 + g, first_pos + warp * 16 + g + 8};
 
   for (int tile = tile_lo; tile <= tile_hi; ++tile) {
@@ -257,7 +261,7 @@ template <int HD>
 static int launch_prefill(const bf16* q, int q_stride, const bf16* k_pages, const bf16* v_pages,
                           const int* block_table, int table_width, const int* seq_start, const int* seq_pos0,
                           bf16* out, int out_stride, int n_seqs, int max_q_len, int H, int K, int hd, int window,
-                          float scale, cudaStream_t stream) {
+                          float scale, const float* sink, cudaStream_t stream) {
   const size_t smem = (size_t)5 * BM * (HD + 8) * sizeof(bf16);
   auto kern = flash_prefill_kernel<HD>;
   if (smem > 48 * 1024) {
@@ -266,14 +270,14 @@ static int launch_prefill(const bf16* q, int q_stride, const bf16* k_pages, cons
   }
   dim3 grid(H * n_seqs, (max_q_len + BM - 1) / BM);
   kern<<<grid, NTHREADS, smem, stream>>>(q, q_stride, k_pages, v_pages, block_table, table_width, seq_start, seq_pos0,
-                                         out, out_stride, H, K, hd, window, scale * 1.4426950408889634f);
+                                         out, out_stride, H, K, hd, window, scale * 1.4426950408889634f, sink);
   RL_LAUNCH_RESULT();
 }
 
 RL_API int rl_flash_prefill(const void* q, int q_stride, const void* k_pages, const void* v_pages,
                             const int* block_table, int table_width, const int* seq_start, const int* seq_pos0,
                             void* out, int out_stride, int n_seqs, int max_q_len, int H, int K, int hd,
-                            int page_size, int window, float scale, cudaStream_t stream) {
+                            int page_size, int window, float scale, const float* sink, cudaStream_t stream) {
   if (n_seqs <= 0 || max_q_len <= 0 || H <= 0 || K <= 0 || hd <= 0)
     RL_REFUSE(1, "flash_prefill: S=%d max_q=%d H=%d K=%d hd=%d", n_seqs, max_q_len, H, K, hd);
   if (H % K) RL_REFUSE(2, "flash_prefill: %d query heads are not a multiple of %d kv heads", H, K);
@@ -289,7 +293,7 @@ RL_API int rl_flash_prefill(const void* q, int q_stride, const void* k_pages, co
   bf16* oo = (bf16*)out;
 #define RL_PREFILL(HDV)                                                                                          \
   return launch_prefill<HDV>(qq, q_stride, kp, vp, block_table, table_width, seq_start, seq_pos0, oo, out_stride, \
-                             n_seqs, max_q_len, H, K, hd, window, scale, stream)
+                             n_seqs, max_q_len, H, K, hd, window, scale, sink, stream)
   if (hd <= 32) RL_PREFILL(32);
   if (hd <= 64) RL_PREFILL(64);
   if (hd <= 128) RL_PREFILL(128);

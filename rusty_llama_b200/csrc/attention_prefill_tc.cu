@@ -201,7 +201,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table, int table_width,
                         const int* __restrict__ seq_start, const int* __restrict__ seq_pos0, bf16* __restrict__ out,
                         int out_stride, int H, int K, int window, float scale_log2, int* __restrict__ status,
-                        int test_role, uint32_t test_ns) {
+                        int test_role, uint32_t test_ns, const float* __restrict__ sink) {
   // All shared memory is dynamic, so that the tiles start at the block's first byte (1024-byte
   // aligned, as the 128-byte swizzle needs) and the small items fit behind them.
   constexpr int SUBS = HD / 64, Q_BYTES = SUBS * SUBQ_BYTES, KV_BYTES = SUBS * SUBK_BYTES;
@@ -377,6 +377,10 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
     const uint32_t o_addr = lane_addr + O_COL;
     float m_run = -INFINITY, l_run = 0.f;   // m_run in units of raw scores times scale_log2
+    if (sink != nullptr) {  // a key without a value whose score is sink[h]: it starts the maximum and counts once in the sum
+      m_run = sink[h] * 1.4426950408889634f;
+      l_run = 1.f;
+    }
     bool ok = true;
     auto give_up = [&](int code) {
       if (lane == 0) {
@@ -511,7 +515,7 @@ template <int HD>
 static int launch_flash_tc(const void* q, int q_stride, int n_tokens, const void* k_pages, const void* v_pages, int n_pages,
                            const int* block_table, int table_width, const int* seq_start, const int* seq_pos0, void* out,
                            int out_stride, int n_seqs, int max_q_len, int H, int K, int window, float scale, int* status,
-                           int wait_test_role, unsigned int wait_test_ns, cudaStream_t stream) {
+                           int wait_test_role, unsigned int wait_test_ns, const float* sink, cudaStream_t stream) {
   CUtensorMap map_q, map_k, map_v;
   if (make_matrix_map(&map_q, q, n_tokens, q_stride, q_stride, BMQ))
     RL_REFUSE(10, "flash_prefill_tc: cannot describe the query tensor to TMA");
@@ -524,7 +528,7 @@ static int launch_flash_tc(const void* q, int q_stride, int n_tokens, const void
   dim3 grid(H * n_seqs, (max_q_len + BMQ - 1) / BMQ);
   RL_LAUNCH_CHECK(rl_launch(kern, grid, NUM_THREADS, smem, stream, map_q, map_k, map_v, block_table, table_width, seq_start, seq_pos0,
                             (bf16*)out, out_stride, H, K, window, scale * 1.4426950408889634f, status, wait_test_role,
-                            (uint32_t)wait_test_ns));
+                            (uint32_t)wait_test_ns, sink));
   return 0;
 }
 
@@ -538,7 +542,7 @@ RL_API int rl_flash_prefill_tc(const void* q, int q_stride, int n_tokens, const 
                                int n_pages, const int* block_table, int table_width, const int* seq_start,
                                const int* seq_pos0, void* out, int out_stride, int n_seqs, int max_q_len, int H, int K,
                                int hd, int page_size, int window, float scale, int* status, int wait_test_role,
-                               unsigned int wait_test_ns, cudaStream_t stream) {
+                               unsigned int wait_test_ns, const float* sink, cudaStream_t stream) {
   if (n_seqs <= 0 || max_q_len <= 0 || H <= 0 || K <= 0 || n_tokens <= 0 || n_pages <= 0)
     RL_REFUSE(1, "flash_prefill_tc: S=%d max_q=%d H=%d K=%d T=%d pages=%d", n_seqs, max_q_len, H, K, n_tokens, n_pages);
   if (!rl_flash_prefill_tc_takes(hd)) RL_REFUSE(2, "flash_prefill_tc: head size %d, this kernel is built for 64 and 128", hd);
@@ -551,7 +555,7 @@ RL_API int rl_flash_prefill_tc(const void* q, int q_stride, int n_tokens, const 
   if (window < 0 || status == nullptr || !(scale > 0.f)) RL_REFUSE(8, "flash_prefill_tc: bad window or scale, or no status word");
   if (hd == 64)
     return launch_flash_tc<64>(q, q_stride, n_tokens, k_pages, v_pages, n_pages, block_table, table_width, seq_start, seq_pos0, out,
-                               out_stride, n_seqs, max_q_len, H, K, window, scale, status, wait_test_role, wait_test_ns, stream);
+                               out_stride, n_seqs, max_q_len, H, K, window, scale, status, wait_test_role, wait_test_ns, sink, stream);
   return launch_flash_tc<128>(q, q_stride, n_tokens, k_pages, v_pages, n_pages, block_table, table_width, seq_start, seq_pos0, out,
-                              out_stride, n_seqs, max_q_len, H, K, window, scale, status, wait_test_role, wait_test_ns, stream);
+                              out_stride, n_seqs, max_q_len, H, K, window, scale, status, wait_test_role, wait_test_ns, sink, stream);
 }

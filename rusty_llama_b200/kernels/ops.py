@@ -304,6 +304,12 @@ def attn_generic(
 ATTN_DECODE_TMA_HEAD_DIMS = (64, 128)  # head sizes the TMA-fed decode kernel is built for
 
 
+def _check_sink(sink, num_heads: int, what: str) -> None:
+    if sink is not None:
+        _cuda(sink, f"{what} sink", torch.float32)
+        _need(sink.numel() == num_heads, f"{what}: one sink per head")
+
+
 def attn_decode_scratch_floats(n_seqs: int, num_heads: int, head_dim: int, n_splits: int) -> int:
     return n_seqs * num_heads * n_splits * (head_dim + 2)
 
@@ -313,9 +319,11 @@ def attn_decode(
     n_splits: int, scratch: torch.Tensor, window: int = 0, scale: Optional[float] = None,
     out: Optional[torch.Tensor] = None, impl: str = "auto", fuse: int = 0,
     inv_freq: Optional[torch.Tensor] = None, rotary_dim: int = 0, interleaved: bool = False,
-    counters: Optional[torch.Tensor] = None,
+    counters: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """One query token per sequence over keys 0..seq_len-1, the key range cut into `n_splits`.
+
+    sink: None, or float32 [H]: exp(sink_h) joins the softmax's denominator of head h and nothing else.
 
     counters (the "tma" kernel only): int32 zeros, one per sequence and group of 8 query heads of a kv
     head; with them the splits are added up by the block that finishes last instead of by a second
@@ -376,6 +384,7 @@ def attn_decode(
         groups = num_kv_heads * ((num_heads // num_kv_heads + 7) // 8)
         _need(counters.numel() >= S * groups, f"attn_decode: {counters.numel()} counters, {S * groups} needed")
     _need(q_parts is None or impl == "tma", "attn_decode: only the TMA kernel takes partial sums")
+    _check_sink(sink, num_heads, "attn_decode")
     if impl == "tma":
         _need(act == torch.bfloat16, "attn_decode: the TMA kernel is bfloat16 only")
         status = _tc_status_word(q.device)
@@ -387,16 +396,16 @@ def attn_decode(
             c_int(n_splits), _p(status), c_int(fuse), _p(inv_freq) if (fuse and rotary_dim) else c_void_p(0), c_int(rotary_dim if fuse else 0),
             c_int(1 if interleaved else 0), _p(counters) if counters is not None else c_void_p(0),
             _p(q_parts) if q_parts is not None else c_void_p(0), c_int(0 if q_parts is None else q_parts.shape[0]),
-            c_ll(0 if q_parts is None else q_parts.stride(0)), *_wt(), _stream(),
+            c_ll(0 if q_parts is None else q_parts.stride(0)), *_wt(), _p(sink), _stream(),
         )
         _check(lib, rc, "attn_decode_tma", kernels=1 if counters is not None else 2)
         return out
     lib = build.load("attention_decode")
-    rc = lib.rl_attn_decode(
+    rc = lib.rl_attn_decode_sink(
         _p(q), c_int(_dt(q, "attn_decode")), c_int(qs), _p(k_pages), _p(v_pages), _p(block_table),
         c_int(block_table.shape[1]), _p(seq_len), part_o, part_ml, _p(out), c_int(out.stride(0)), c_int(S),
         c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(PAGE_SIZE), c_int(window), c_float(scale),
-        c_int(n_splits), _stream(),
+        c_int(n_splits), _p(sink), _stream(),
     )
     _check(lib, rc, "attn_decode", kernels=2)
     return out
@@ -405,9 +414,9 @@ def attn_decode(
 def flash_prefill(
     q: torch.Tensor, k_pages, v_pages, block_table, seq_start, seq_pos0, max_q_len: int, num_heads: int,
     num_kv_heads: int, head_dim: int, window: int = 0, scale: Optional[float] = None,
-    out: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
-    """bfloat16 causal attention of a ragged batch over the paged cache (tensor cores)."""
+    """bfloat16 causal attention of a ragged batch over the paged cache (tensor cores).  sink: None, or float32 [H] (see `attn_decode`)."""
     _cuda(q, "flash_prefill q", torch.bfloat16, contiguous=False)
     qs = _rows(q, "flash_prefill q")
     T = q.shape[0]
@@ -424,11 +433,12 @@ def flash_prefill(
     _cuda(out, "flash_prefill out", torch.bfloat16)
     if scale is None:
         scale = 1.0 / math.sqrt(head_dim)
+    _check_sink(sink, num_heads, "flash_prefill")
     lib = build.load("attention_prefill")
     rc = lib.rl_flash_prefill(
         _p(q), c_int(qs), _p(k_pages), _p(v_pages), _p(block_table), c_int(block_table.shape[1]), _p(seq_start),
         _p(seq_pos0), _p(out), c_int(out.stride(0)), c_int(S), c_int(max_q_len), c_int(num_heads),
-        c_int(num_kv_heads), c_int(head_dim), c_int(PAGE_SIZE), c_int(window), c_float(scale), _stream(),
+        c_int(num_kv_heads), c_int(head_dim), c_int(PAGE_SIZE), c_int(window), c_float(scale), _p(sink), _stream(),
     )
     _check(lib, rc, "flash_prefill")
     return out
@@ -440,7 +450,7 @@ FLASH_TC_HEAD_DIMS = (64, 128)  # head sizes the tcgen05 prompt attention is bui
 def flash_prefill_tc(
     q: torch.Tensor, k_pages, v_pages, block_table, seq_start, seq_pos0, max_q_len: int, num_heads: int,
     num_kv_heads: int, head_dim: int, window: int = 0, scale: Optional[float] = None,
-    out: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """`flash_prefill` on the tcgen05 tensor cores (TMA-fed, S and P V in tensor memory); head sizes 64 and 128."""
     _need(head_dim in FLASH_TC_HEAD_DIMS, f"flash_prefill_tc: head size {head_dim}, this kernel is built for {FLASH_TC_HEAD_DIMS}")
@@ -460,12 +470,13 @@ def flash_prefill_tc(
     _cuda(out, "flash_prefill_tc out", torch.bfloat16)
     if scale is None:
         scale = 1.0 / math.sqrt(head_dim)
+    _check_sink(sink, num_heads, "flash_prefill_tc")
     status = _tc_status_word(q.device)
     lib = build.load("attention_prefill_tc")
     rc = lib.rl_flash_prefill_tc(
         _p(q), c_int(qs), c_int(T), _p(k_pages), _p(v_pages), c_int(k_pages.shape[0]), _p(block_table),
         c_int(block_table.shape[1]), _p(seq_start), _p(seq_pos0), _p(out), c_int(out.stride(0)), c_int(S), c_int(max_q_len),
-        c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(PAGE_SIZE), c_int(window), c_float(scale), _p(status), *_wt(), _stream(),
+        c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(PAGE_SIZE), c_int(window), c_float(scale), _p(status), *_wt(), _p(sink), _stream(),
     )
     _check(lib, rc, "flash_prefill_tc")
     return out

@@ -66,9 +66,10 @@ class Attention(Mixer):
              q, k, v (and the gate) are kept as one matrix so that one product
              serves them all (src/backend/cuda.rs:423-442).
 
-    A plain attention runs on the kernels built for it (tensor-core prompt attention, TMA-fed decode attention, the rotation
-    fused with the cache write or with the decode kernel).  With any of the options it runs on `qkv_prep` and `attn_ext`
-    (csrc/attention_ext.cu), which take every option and both element types."""
+    A plain attention, with or without a sink, runs on the kernels built for it (tensor-core prompt attention, TMA-fed
+    decode attention, the rotation fused with the cache write or with the decode kernel).  With any other option, in a 32-bit run
+    with a sink, or with a head size that is no multiple of 8 it runs on `qkv_prep` and `attn_ext` (csrc/attention_ext.cu),
+    which take every option, every size and both element types."""
 
     takes_out = True
 
@@ -93,24 +94,25 @@ class Attention(Mixer):
             raise ConfigError("attention: 'position' must be a PartSpec")
         self.position = POSITIONS.build(pos_spec, runtime)
         magnitude = float(getattr(self.position, "magnitude", 1.0))
-        self.extended = (self.vd != self.hd or self.has_sink or self.has_mix or self.has_gate or self.has_bias
-                         or self.out_scale != 1.0 or magnitude != 1.0)
+        # what the kernels built for a plain attention take: equal key and value sizes, at most a sink beside the plain softmax
+        # (the 32-bit attention kernel has none), and in bfloat16 a head size that moves in 16-byte pieces
+        plain = self.vd == self.hd and not (self.has_mix or self.has_gate or self.has_bias) and self.out_scale == 1.0 and magnitude == 1.0
+        if plain and self.has_sink:
+            plain = runtime.dtype != torch.float32 and self.hd % 8 == 0
+        self.extended = not plain
+        if max(self.hd, self.vd) > 256:
+            raise ConfigError(f"attention: head sizes {self.hd} / {self.vd} are above 256, the most the attention kernels built here take")
         if self.extended:
-            if max(self.hd, self.vd) > 256:
-                raise ConfigError(f"attention: head sizes {self.hd} / {self.vd} are above 256, the most the attention kernels built here take")
             if self.has_mix and self.H > 32:
                 raise ConfigError(f"attention: the scores of {self.H} heads cannot be mixed, the kernel built here takes 32")
             rotary_dim = int(getattr(self.position, "rotary_dim", 0))
             if rotary_dim and not hasattr(self.position, "inv_freq"):
                 raise ConfigError("attention: with its options the mixer rotates by a frequency table itself and needs a 'rotary' position part (or none)")
             self.rotation = (getattr(self.position, "inv_freq", None), rotary_dim, bool(getattr(self.position, "interleaved", False)), magnitude)
-        else:
-            if self.hd > 256:
-                raise ConfigError(f"attention: head_dim {self.hd} is above 256, the most the attention kernels built here take")
-            if self.hd % 8 and runtime.dtype != torch.float32:
-                raise ConfigError(
-                    f"attention: the bfloat16 kernels move a head in 16-byte pieces and need head_dim to be a multiple of 8, got {self.hd} "
-                    f"(a float32 run takes any head size up to 256)")
+        elif self.hd % 8 and runtime.dtype != torch.float32:
+            raise ConfigError(
+                f"attention: the bfloat16 kernels move a head in 16-byte pieces and need head_dim to be a multiple of 8, got {self.hd} "
+                f"(a float32 run takes any head size up to 256)")
         self.scale = float(spec.params.get("scale") or 1.0 / math.sqrt(self.hd))
         self.qd, self.kvd, self.vvd, self.od = self.H * self.hd, self.K * self.hd, self.K * self.vd, self.H * self.vd
         self.w_qkv = None
@@ -222,18 +224,18 @@ class Attention(Mixer):
                 counters = self.rt.workspace.get("attn_decode_counters", step.n_seqs * groups, torch.int32, zeroed=True)
             a = ops.attn_decode(
                 qkv, cache.k_pages, cache.v_pages, cache.block_table, step.seq_len, self.H, self.K, self.hd,
-                n_splits, scratch, window=self.window, scale=self.scale, counters=counters,
+                n_splits, scratch, window=self.window, scale=self.scale, counters=counters, sink=self.sink,
                 **({} if fusion is None else dict(
                     fuse=1 if shared_cache else 2, inv_freq=fusion[0], rotary_dim=fusion[1], interleaved=fusion[2])),
             )
         elif self.hd in ops.FLASH_TC_HEAD_DIMS:
             a = ops.flash_prefill_tc(
                 qkv, cache.k_pages, cache.v_pages, cache.block_table, step.seq_start, step.seq_pos0,
-                step.max_q_len, self.H, self.K, self.hd, window=self.window, scale=self.scale,
+                step.max_q_len, self.H, self.K, self.hd, window=self.window, scale=self.scale, sink=self.sink,
             )
         else:
             a = ops.flash_prefill(
                 qkv, cache.k_pages, cache.v_pages, cache.block_table, step.seq_start, step.seq_pos0,
-                step.max_q_len, self.H, self.K, self.hd, window=self.window, scale=self.scale,
+                step.max_q_len, self.H, self.K, self.hd, window=self.window, scale=self.scale, sink=self.sink,
             )
         return a, self.w_o

@@ -542,3 +542,41 @@ def test_row_kernels(dtype):
     assert np.abs(xt.to(torch.float64).cpu().numpy() - x_ref).max() <= 2e-5
     ref = pr.centred_norm(x_ref, wn - 1.0, 1e-6)
     assert np.abs(out.to(torch.float64).cpu().numpy() - ref).max() <= _tol(dtype, 1e-5, 2e-2) * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("hd, H, G", [(64, 8, 2), (128, 4, 4), (48, 6, 3), (24, 2, 1)])
+def test_sink_on_the_tensor_core_attention_kernels(hd, H, G):
+    """The bfloat16 kernels of a plain attention with a sink: a prompt that goes on from position 70 with 90 tokens (both prompt
+    kernels where the head size allows), then single tokens at positions around page borders with the key range in one part
+    and in several (both decode kernels).  Sinks of the size of the scores, one very large, one very small."""
+    from rusty_llama_b200.kernels import ops
+
+    rng = np.random.default_rng(hd)
+    dt, L = torch.bfloat16, 64 * 5
+    k = _rounded(rng.standard_normal((L, G, hd)), dt)
+    v = _rounded(rng.standard_normal((L, G, hd)), dt)
+    sink = np.concatenate([[30.0, -30.0], 2.0 * rng.standard_normal(H)])[:H] if H > 2 else np.array([1.0, 30.0])
+    scale = 0.9 / np.sqrt(hd)
+    kp, vp, table = _paged_kv(k, v, dt, 7, [5, 0, 3, 6, 2])
+    sink_t = _dev(sink, torch.float32)
+    q_all = _rounded(rng.standard_normal((L, H, hd)), dt)
+    ref = pr.softmax_attention(q_all, k, v, scale, 0, sink, None)
+    # prompt: rows 70 .. 159
+    q = _dev(q_all[70:160].reshape(90, H * hd), dt)
+    start, pos0 = _i32([0, 90]), _i32([70])
+    outs = {"flash_prefill": ops.flash_prefill(q, kp, vp, table, start, pos0, 90, H, G, hd, scale=scale, sink=sink_t)}
+    if hd in ops.FLASH_TC_HEAD_DIMS:
+        outs["flash_prefill_tc"] = ops.flash_prefill_tc(q, kp, vp, table, start, pos0, 90, H, G, hd, scale=scale, sink=sink_t)
+    for name, out in outs.items():
+        err = np.abs(out.to(torch.float64).cpu().numpy() - ref[70:160]).max()
+        assert err <= 2e-2 * max(1.0, np.abs(ref).max()), (name, err)
+    # decoding
+    for p in (0, 1, 63, 64, 65, 200, 319):
+        qd = _dev(q_all[p : p + 1].reshape(1, H * hd), dt)
+        for impl in ("warp",) + (("tma",) if hd in ops.ATTN_DECODE_TMA_HEAD_DIMS else ()):
+            for n_splits in (1, 3):
+                scratch = torch.empty(ops.attn_decode_scratch_floats(1, H, hd, n_splits), dtype=torch.float32, device="cuda")
+                out = ops.attn_decode(qd, kp, vp, table, _i32([p + 1]), H, G, hd, n_splits, scratch, scale=scale, impl=impl, sink=sink_t)
+                err = np.abs(out.to(torch.float64).cpu().numpy()[0] - ref[p]).max()
+                assert err <= 2e-2 * max(1.0, np.abs(ref).max()), (impl, n_splits, p, err)
+    ops.tc_status_check()
