@@ -1,0 +1,330 @@
+// bfloat16 flash attention on the tensor cores (mma.sync m16n8k16) for the attention with options: keys and values of unequal
+// sizes, a window, a sink, a gate and a constant factor on the result, and scores that are mixed across heads before the softmax.
+//
+// Mixed scores.  s'_h = sum_g mix[h][g] (q_g . k_kv(g)) is linear in the queries, so it is the score of ONE longer query
+// against the keys of all kv heads side by side:
+//     s'_h = sum_c Q'[h][c] . k_c,    Q'[h][c] = sum_{g in group c} mix[h][g] q_g        (c = kv head)
+// `fold_queries` makes Q' (32-bit sums of the rotated queries, stored as bfloat16); the attention kernel then adds the partial
+// products of a head's parts c = 0 .. K-1 into one accumulator and goes on as any flash attention does.  Without a mixing
+// matrix a head has one part, its own kv head's keys.
+//
+// A block of four warps owns 64 query rows of one head of one sequence.  A key tile is one cache page.  The loads of a tile
+// are, in order, the keys of each part and then the values; they go through a ring of three buffers with cp.async, two loads
+// ahead of the one in use.  The online softmax (max, sum, rescale) is 32-bit, in base-2 exponents.  Sizes are padded with
+// zeros to HD in shared memory, so key and value sizes in multiples of 8 up to 256 are served.  Prompts and single tokens
+// alike: a decode step is a batch of sequences with one query row each.
+#include "common.cuh"
+
+RL_DEFINE_ERROR_TEXT()
+
+#define BM 64   // query rows per block
+#define BN 64   // keys per tile = page size
+#define NTHREADS 128
+#define NBUF 3
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(a));
+}
+// d += a(16x16, row) * b(16x8, col)
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// ---------------------------------------------------------------- folded queries
+// out[t][h][c][i] = sum over the heads g of kv head c of mix[h][g] * q[t][g][i], in 32-bit, stored as bfloat16.
+__global__ void fold_queries_kernel(const bf16* __restrict__ q, int q_stride, const float* __restrict__ mix, bf16* __restrict__ out, int H,
+                                    int K, int kdim) {
+  const int t = blockIdx.x, rep = H / K;
+  const bf16* row = q + (size_t)t * q_stride;
+  bf16* o = out + (size_t)t * H * K * kdim;
+  for (int idx = threadIdx.x; idx < H * K * kdim; idx += blockDim.x) {
+    const int i = idx % kdim, c = (idx / kdim) % K, h = idx / (kdim * K);
+    float acc = 0.f;
+    for (int g = c * rep; g < (c + 1) * rep; ++g) acc += mix[h * H + g] * __bfloat162float(row[(size_t)g * kdim + i]);
+    o[idx] = __float2bfloat16_rn(acc);
+  }
+}
+
+RL_API int rl_fold_queries(const void* q, int q_stride, const float* mix, void* out, int n_tokens, int H, int K, int kdim,
+                           cudaStream_t stream) {
+  if (n_tokens <= 0 || H <= 0 || K <= 0 || kdim <= 0 || H % K || !q || !mix || !out) RL_REFUSE(1, "fold_queries: T=%d H=%d K=%d kdim=%d", n_tokens, H, K, kdim);
+  fold_queries_kernel<<<n_tokens, 256, 0, stream>>>((const bf16*)q, q_stride, mix, (bf16*)out, H, K, kdim);
+  RL_LAUNCH_RESULT();
+}
+
+// ---------------------------------------------------------------- the attention
+// Copy rows [n_rows][width] (row stride src_stride) into rows of `stride` elements; width a multiple of 8.
+__device__ __forceinline__ void load_rows(bf16* dst, const bf16* src, size_t src_stride, int n_rows, int width, int stride) {
+  const int chunks = width >> 3;
+  for (int c = threadIdx.x; c < n_rows * chunks; c += NTHREADS) {
+    const int r = c / chunks, cc = c - r * chunks;
+    cp_async_16(dst + (size_t)r * stride + cc * 8, src + (size_t)r * src_stride + cc * 8);
+  }
+}
+
+template <int HD>
+__global__ void __launch_bounds__(NTHREADS)
+flash_mix_kernel(const bf16* __restrict__ q, long long q_row_stride, int q_head_stride, int parts, const bf16* __restrict__ k_pages,
+                 const bf16* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
+                 const int* __restrict__ seq_start, const int* __restrict__ seq_pos0, const float* __restrict__ sink,
+                 const bf16* __restrict__ gate, int gate_stride, float out_scale, bf16* __restrict__ out, int out_stride, int H, int K,
+                 int kdim, int vdim, int window, float scale_log2) {
+  constexpr int STRIDE = HD + 8;  // 16 bytes of padding per row keep ldmatrix free of bank conflicts
+  constexpr int KSTEPS = HD / 16;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* ring = reinterpret_cast<bf16*>(smem_raw);  // NBUF x [BN][STRIDE]
+  bf16* q_s = ring + NBUF * BN * STRIDE;           // parts x [BM][STRIDE]
+
+  const int s = blockIdx.x / H, h = blockIdx.x % H;
+  const int tok0 = seq_start[s];
+  const int q_len = seq_start[s + 1] - tok0;
+  const int row0 = (int)(gridDim.y - 1 - blockIdx.y) * BM;  // the row tiles with the most keys start first
+  if (row0 >= q_len) return;
+  const int pos0 = seq_pos0[s];
+  const int kh = h / (H / K);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int rows_here = min(BM, q_len - row0);
+
+  // ---- zero everything once (padding columns, rows past the end), then load the query parts
+  {
+    uint4 z = make_uint4(0, 0, 0, 0);
+    uint4* p = reinterpret_cast<uint4*>(smem_raw);
+    const int n16 = ((NBUF * BN + parts * BM) * STRIDE * (int)sizeof(bf16)) / 16;
+    for (int i = tid; i < n16; i += NTHREADS) p[i] = z;
+  }
+  __syncthreads();
+  for (int p = 0; p < parts; ++p)
+    load_rows(q_s + (size_t)p * BM * STRIDE, q + (size_t)(tok0 + row0) * q_row_stride + (size_t)h * q_head_stride + (size_t)p * kdim,
+              (size_t)q_row_stride, rows_here, kdim, STRIDE);
+  const int* table = block_table + (size_t)s * table_width;
+  const int last_pos = pos0 + row0 + rows_here - 1;
+  const int first_pos = pos0 + row0;
+  const int lowest_key = (window != 0 && first_pos + 1 > window) ? first_pos + 1 - window : 0;
+  const int tile_lo = lowest_key / BN, tile_hi = last_pos / BN;
+  const int per_tile = parts + 1;
+  const int n_loads = (tile_hi - tile_lo + 1) * per_tile;
+  auto issue = [&](int n) {
+    const int tile = tile_lo + n / per_tile, part = n % per_tile;
+    bf16* dst = ring + (size_t)(n % NBUF) * BN * STRIDE;
+    const size_t page = (size_t)table[tile];
+    if (part < parts) {
+      const int kv = parts > 1 ? part : kh;
+      load_rows(dst, k_pages + ((page * K + kv) * BN) * kdim, (size_t)kdim, BN, kdim, STRIDE);
+    } else {
+      load_rows(dst, v_pages + ((page * K + kh) * BN) * vdim, (size_t)vdim, BN, vdim, STRIDE);
+    }
+  };
+  issue(0);
+  cp_async_commit();  // (the queries travel in this group too)
+  if (n_loads > 1) issue(1);
+  cp_async_commit();
+
+  float o_acc[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.f, 0.f};  // per-thread partial sums, reduced over the quad at the end
+  if (sink != nullptr) {        // a key without a value whose score is sink[h]
+    m_run[0] = m_run[1] = sink[h] * 1.4426950408889634f;
+    l_run[0] = l_run[1] = (t4 == 0) ? 1.f : 0.f;
+  }
+  const int qpos[2] = {first_pos + warp * 16 + g, first_pos + warp * 16 + g + 8};
+  float s_acc[BN / 8][4];
+
+  for (int n = 0; n < n_loads; ++n) {
+    if (n + 2 < n_loads) issue(n + 2);
+    cp_async_commit();  // (an empty group where nothing was issued keeps the count of groups in step)
+    cp_async_wait<2>();
+    __syncthreads();
+    const int tile = tile_lo + n / per_tile, part = n % per_tile;
+    const bf16* buf = ring + (size_t)(n % NBUF) * BN * STRIDE;
+    if (part < parts) {
+      // ---- S (+)= Q_part K^T for this warp's 16 rows and the tile's 64 keys
+      if (part == 0) {
+#pragma unroll
+        for (int i = 0; i < BN / 8; ++i) s_acc[i][0] = s_acc[i][1] = s_acc[i][2] = s_acc[i][3] = 0.f;
+      }
+      const bf16* qp = q_s + (size_t)part * BM * STRIDE;
+#pragma unroll
+      for (int kk = 0; kk < KSTEPS; ++kk) {
+        uint32_t a[4];
+        ldmatrix_x4(a, qp + (size_t)(warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * STRIDE + kk * 16 + 8 * (lane >> 4));
+#pragma unroll
+        for (int np = 0; np < BN / 16; ++np) {
+          uint32_t b[4];
+          ldmatrix_x4(b, buf + (size_t)(np * 16 + (lane & 7) + 8 * (lane >> 4)) * STRIDE + kk * 16 + 8 * ((lane >> 3) & 1));
+          mma_bf16(s_acc[2 * np], a, b[0], b[1]);
+          mma_bf16(s_acc[2 * np + 1], a, b[2], b[3]);
+        }
+      }
+    } else {
+      // ---- mask, scale (to base-2 exponents) and the online softmax
+      const int key0 = tile * BN;
+      float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int nn = 0; nn < BN / 8; ++nn) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int r = e >> 1;
+          float v = s_acc[nn][e] * scale_log2;
+          const int key = key0 + nn * 8 + 2 * t4 + (e & 1);
+          const bool seen = key <= qpos[r] && (window == 0 || qpos[r] - key < window);
+          if (!seen) v = -INFINITY;
+          s_acc[nn][e] = v;
+          tile_max[r] = fmaxf(tile_max[r], v);
+        }
+      }
+      float alpha[2], m_use[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        float mx = tile_max[r];
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run[r], mx);
+        m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;  // a row that has seen no key yet keeps exponent base 0
+        alpha[r] = exp2f(m_run[r] - m_use[r]);
+        m_run[r] = m_new;
+        l_run[r] *= alpha[r];
+      }
+#pragma unroll
+      for (int nn = 0; nn < BN / 8; ++nn) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int r = e >> 1;
+          const float p = exp2f(s_acc[nn][e] - m_use[r]);
+          s_acc[nn][e] = p;
+          l_run[r] += p;
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < HD / 8; ++i) {
+        o_acc[i][0] *= alpha[0];
+        o_acc[i][1] *= alpha[0];
+        o_acc[i][2] *= alpha[1];
+        o_acc[i][3] *= alpha[1];
+      }
+      // ---- O += P V
+#pragma unroll
+      for (int kk = 0; kk < BN / 16; ++kk) {
+        uint32_t a[4];
+        a[0] = pack_bf16(s_acc[2 * kk][0], s_acc[2 * kk][1]);
+        a[1] = pack_bf16(s_acc[2 * kk][2], s_acc[2 * kk][3]);
+        a[2] = pack_bf16(s_acc[2 * kk + 1][0], s_acc[2 * kk + 1][1]);
+        a[3] = pack_bf16(s_acc[2 * kk + 1][2], s_acc[2 * kk + 1][3]);
+#pragma unroll
+        for (int dp = 0; dp < HD / 16; ++dp) {
+          uint32_t b[4];
+          ldmatrix_x4_trans(b, buf + (size_t)(kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * STRIDE + dp * 16 + 8 * (lane >> 4));
+          mma_bf16(o_acc[2 * dp], a, b[0], b[1]);
+          mma_bf16(o_acc[2 * dp + 1], a, b[2], b[3]);
+        }
+      }
+    }
+    __syncthreads();  // all warps done with this buffer before it is refilled
+  }
+
+  // ---- normalise, gate, scale and store
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    float l = l_run[r];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    const float inv = (l > 0.f) ? out_scale / l : 0.f;
+    const int row = warp * 16 + g + 8 * r;
+    if (row < rows_here) {
+      const size_t t = (size_t)(tok0 + row0 + row);
+      bf16* o = out + t * out_stride + (size_t)h * vdim;
+      const bf16* gr = gate ? gate + t * gate_stride + (size_t)h * vdim : nullptr;
+#pragma unroll
+      for (int nn = 0; nn < HD / 8; ++nn) {
+        const int d = nn * 8 + 2 * t4;
+        if (d < vdim) {
+          float a0 = o_acc[nn][2 * r] * inv, a1 = o_acc[nn][2 * r + 1] * inv;
+          if (gr) {
+            a0 *= 1.0f / (1.0f + expf(-__bfloat162float(gr[d])));
+            a1 *= 1.0f / (1.0f + expf(-__bfloat162float(gr[d + 1])));
+          }
+          *reinterpret_cast<__nv_bfloat162*>(o + d) = __floats2bfloat162_rn(a0, a1);
+        }
+      }
+    }
+  }
+}
+
+RL_API int rl_flash_mix_smem(int hd_max, int parts) {
+  const int HD = hd_max <= 32 ? 32 : (hd_max <= 64 ? 64 : (hd_max <= 128 ? 128 : 256));
+  return (NBUF * BN + parts * BM) * (HD + 8) * (int)sizeof(bf16);
+}
+
+template <int HD>
+static int launch_mix(const bf16* q, long long q_row_stride, int q_head_stride, int parts, const bf16* k_pages, const bf16* v_pages,
+                      const int* block_table, int table_width, const int* seq_start, const int* seq_pos0, const float* sink,
+                      const bf16* gate, int gate_stride, float out_scale, bf16* out, int out_stride, int n_seqs, int max_q_len, int H, int K,
+                      int kdim, int vdim, int window, float scale, cudaStream_t stream) {
+  const size_t smem = (size_t)(NBUF * BN + parts * BM) * (HD + 8) * sizeof(bf16);
+  auto kern = flash_mix_kernel<HD>;
+  if (smem > 227 * 1024) RL_REFUSE(8, "flash_mix: %zu bytes of shared memory for %d query parts exceed the SM's", smem, parts);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) RL_REFUSE(8, "flash_mix: cannot get %zu bytes of shared memory", smem);
+  }
+  dim3 grid(H * n_seqs, (max_q_len + BM - 1) / BM);
+  kern<<<grid, NTHREADS, smem, stream>>>(q, q_row_stride, q_head_stride, parts, k_pages, v_pages, block_table, table_width, seq_start,
+                                         seq_pos0, sink, gate, gate_stride, out_scale, out, out_stride, H, K, kdim, vdim, window,
+                                         scale * 1.4426950408889634f);
+  RL_LAUNCH_RESULT();
+}
+
+// q: the queries [T][..], row stride q_row_stride, head h at h * q_head_stride, part p of a head at + p * kdim.
+// parts: 1 (a head reads its own kv head's keys) or K (folded queries: part c goes against the keys of kv head c).
+RL_API int rl_flash_mix(const void* q, long long q_row_stride, int q_head_stride, int parts, const void* k_pages, const void* v_pages,
+                        const int* block_table, int table_width, const int* seq_start, const int* seq_pos0, const float* sink,
+                        const void* gate, int gate_stride, float out_scale, void* out, int out_stride, int n_seqs, int max_q_len, int H,
+                        int K, int kdim, int vdim, int page_size, int window, float scale, cudaStream_t stream) {
+  if (n_seqs <= 0 || max_q_len <= 0 || H <= 0 || K <= 0 || kdim <= 0 || vdim <= 0)
+    RL_REFUSE(1, "flash_mix: S=%d max_q=%d H=%d K=%d kdim=%d vdim=%d", n_seqs, max_q_len, H, K, kdim, vdim);
+  if (H % K) RL_REFUSE(2, "flash_mix: %d query heads are not a multiple of %d kv heads", H, K);
+  if (page_size != BN) RL_REFUSE(3, "flash_mix: page size %d, this kernel is built for %d", page_size, BN);
+  if (kdim % 8 || vdim % 8) RL_REFUSE(4, "flash_mix: key and value sizes %d / %d must be multiples of 8", kdim, vdim);
+  if (q_row_stride % 8 || q_head_stride % 8 || out_stride % 2 || gate_stride % 2 || ((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages) % 16 ||
+      ((uintptr_t)out | (uintptr_t)gate) % 4)
+    RL_REFUSE(5, "flash_mix: strides or addresses break the alignment of 16-byte copies and paired stores");
+  if ((long long)H * n_seqs > 0x7fffffffLL || max_q_len / 16 > 65535) RL_REFUSE(6, "flash_mix: the grid is too large");
+  if (window < 0 || (parts != 1 && parts != K)) RL_REFUSE(7, "flash_mix: window %d, parts %d of %d kv heads", window, parts, K);
+  const int hd = kdim > vdim ? kdim : vdim;
+#define RL_MIX(HDV)                                                                                                                   \
+  return launch_mix<HDV>((const bf16*)q, q_row_stride, q_head_stride, parts, (const bf16*)k_pages, (const bf16*)v_pages, block_table,  \
+                         table_width, seq_start, seq_pos0, sink, (const bf16*)gate, gate_stride, out_scale, (bf16*)out, out_stride,      \
+                         n_seqs, max_q_len, H, K, kdim, vdim, window, scale, stream)
+  if (hd <= 32) RL_MIX(32);
+  if (hd <= 64) RL_MIX(64);
+  if (hd <= 128) RL_MIX(128);
+  if (hd <= 256) RL_MIX(256);
+#undef RL_MIX
+  RL_REFUSE(9, "flash_mix: head size %d exceeds 256", hd);
+}

@@ -1437,3 +1437,73 @@ def unary_act(x: torch.Tensor, kind: int = ACT_RELU2) -> torch.Tensor:
     rc = lib.rl_unary_act(_p(x), _p(out), c_int(_dt(x, "unary_act")), c_ll(x.numel()), c_int(kind), _stream())
     _check(lib, rc, "unary_act")
     return out
+
+
+# ------------------------------------------------------------------ tensor-core attention with options (csrc/attention_mix_mma.cu)
+FLASH_MIX_SMEM_LIMIT = 227 * 1024
+
+
+def flash_mix_takes(kdim: int, vdim: int, parts: int) -> bool:
+    """Whether `flash_mix` is built for these sizes: multiples of 8 up to 256, and the query parts fit shared memory."""
+    if kdim % 8 or vdim % 8 or max(kdim, vdim) > 256:
+        return False
+    hd = max(kdim, vdim)
+    hd = 32 if hd <= 32 else 64 if hd <= 64 else 128 if hd <= 128 else 256
+    return (3 * 64 + parts * 64) * (hd + 8) * 2 <= FLASH_MIX_SMEM_LIMIT
+
+
+def fold_queries(q: torch.Tensor, mix: torch.Tensor, num_heads: int, num_kv_heads: int, kdim: int) -> torch.Tensor:
+    """out[t, h, c, :] = sum over the heads g of kv head c of mix[h, g] * q[t, g, :] (32-bit sums, bfloat16 result): the queries
+    with which head h's mixed score is one product against the keys of all kv heads side by side."""
+    _cuda(q, "fold_queries q", torch.bfloat16, contiguous=False)
+    qs = _rows(q, "fold_queries q")
+    _need(q.shape[1] >= num_heads * kdim, "fold_queries: q rows too short")
+    _cuda(mix, "fold_queries mix", torch.float32)
+    _need(tuple(mix.shape) == (num_heads, num_heads), "fold_queries: the mixing matrix must be [H, H]")
+    T = q.shape[0]
+    out = torch.empty((T, num_heads * num_kv_heads * kdim), dtype=torch.bfloat16, device=q.device)
+    lib = build.load("attention_mix_mma")
+    rc = lib.rl_fold_queries(_p(q), c_int(qs), _p(mix), _p(out), c_int(T), c_int(num_heads), c_int(num_kv_heads), c_int(kdim), _stream())
+    _check(lib, rc, "fold_queries")
+    return out
+
+
+def flash_mix(
+    q: torch.Tensor, k_pages, v_pages, block_table, seq_start, seq_pos0, max_q_len: int, num_heads: int, num_kv_heads: int, kdim: int,
+    vdim: int, scale: float, window: int = 0, sink: Optional[torch.Tensor] = None, folded: bool = False, gate: Optional[torch.Tensor] = None,
+    out_scale: float = 1.0, out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """bfloat16 attention of a ragged batch over the paged cache on the tensor cores, keys of `kdim` and values of `vdim` numbers,
+    with a window, a sink, a gate (out *= sigmoid(gate)) and a constant factor.  folded: q is what `fold_queries` made
+    ([T, H K kdim]: the heads' scores are mixed); else q holds [T, >= H kdim] rows."""
+    _cuda(q, "flash_mix q", torch.bfloat16, contiguous=False)
+    qs = _rows(q, "flash_mix q")
+    T = q.shape[0]
+    parts = num_kv_heads if folded else 1
+    _need(q.shape[1] >= num_heads * parts * kdim, "flash_mix: q rows too short")
+    _need(flash_mix_takes(kdim, vdim, parts), f"flash_mix: sizes {kdim} / {vdim} with {parts} query parts are not built")
+    _check_kv_pages(k_pages, v_pages, torch.bfloat16, num_kv_heads, kdim, vdim, "flash_mix")
+    _cuda(block_table, "flash_mix block_table", torch.int32)
+    _cuda(seq_start, "flash_mix seq_start", torch.int32)
+    _cuda(seq_pos0, "flash_mix seq_pos0", torch.int32)
+    S = seq_pos0.numel()
+    _need(seq_start.numel() == S + 1 and block_table.dim() == 2 and block_table.shape[0] >= S, "flash_mix: metadata sizes")
+    _check_sink(sink, num_heads, "flash_mix")
+    gs = 0
+    if gate is not None:
+        _cuda(gate, "flash_mix gate", torch.bfloat16, contiguous=False)
+        gs = _rows(gate, "flash_mix gate")
+        _need(gate.shape[0] == T and gate.shape[1] >= num_heads * vdim, "flash_mix: gate rows too short")
+    if out is None:
+        out = torch.empty((T, num_heads * vdim), dtype=torch.bfloat16, device=q.device)
+    _cuda(out, "flash_mix out", torch.bfloat16, contiguous=False)
+    _need(tuple(out.shape) == (T, num_heads * vdim) and _rows(out, "flash_mix out") >= num_heads * vdim, "flash_mix: out must be [T, H vdim]")
+    lib = build.load("attention_mix_mma")
+    rc = lib.rl_flash_mix(
+        _p(q), c_ll(qs), c_int(parts * kdim), c_int(parts), _p(k_pages), _p(v_pages), _p(block_table), c_int(block_table.shape[1]),
+        _p(seq_start), _p(seq_pos0), _p(sink), _p(gate), c_int(gs), c_float(out_scale), _p(out), c_int(out.stride(0)), c_int(S),
+        c_int(max_q_len), c_int(num_heads), c_int(num_kv_heads), c_int(kdim), c_int(vdim), c_int(PAGE_SIZE), c_int(window), c_float(scale),
+        _stream(),
+    )
+    _check(lib, rc, "flash_mix")
+    return out

@@ -176,6 +176,17 @@ class Attention(Mixer):
             self.H, self.K, self.hd, self.vd, rotary_dim, interleaved,
         )
         gate = proj[:, self.qd + self.kvd + self.vvd :] if self.has_gate else None
+        parts = self.K if self.has_mix else 1
+        if (self.rt.dtype == torch.bfloat16 and ops.flash_mix_takes(self.hd, self.vd, parts) and proj.stride(0) % 8 == 0
+                and (out is None or (out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0)) and (self.qd + self.kvd + self.vvd) % 2 == 0):
+            # the tensor-core kernel, for prompts and single tokens alike; mixed scores come from folded queries
+            q = ops.fold_queries(proj, self.mix, self.H, self.K, self.hd) if self.has_mix else proj
+            a = ops.flash_mix(
+                q, cache.k_pages, cache.v_pages, cache.block_table, step.seq_start, step.seq_pos0, step.max_q_len, self.H, self.K,
+                self.hd, self.vd, self.scale, window=self.window, sink=self.sink, folded=self.has_mix, gate=gate, out_scale=self.out_scale,
+                out=out,
+            )
+            return a, self.w_o
         a = ops.attn_ext(
             proj, cache.k_pages, cache.v_pages, cache.block_table, step.tok_seq, step.tok_pos, self.H, self.K, self.hd, self.vd,
             self.scale, window=self.window, sink=self.sink, mix=self.mix, gate=gate, out_scale=self.out_scale, out=out,

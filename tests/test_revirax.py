@@ -580,3 +580,64 @@ def test_sink_on_the_tensor_core_attention_kernels(hd, H, G):
                 err = np.abs(out.to(torch.float64).cpu().numpy()[0] - ref[p]).max()
                 assert err <= 2e-2 * max(1.0, np.abs(ref).max()), (impl, n_splits, p, err)
     ops.tc_status_check()
+
+
+@pytest.mark.parametrize("H, G, kd, vd, window, talk, use_sink", [
+    (4, 2, 32, 32, 40, True, False), (8, 4, 16, 24, 5, True, False), (2, 1, 96, 96, 64, True, False), (6, 2, 24, 8, 0, False, True),
+    (4, 4, 128, 64, 65, True, True), (1, 1, 8, 200, 0, False, False), (16, 8, 64, 64, 100, True, False)])
+def test_tensor_core_attention_with_options(H, G, kd, vd, window, talk, use_sink):
+    """`flash_mix` on a ragged step (a sequence that goes on from position 70 with 100 tokens, one that starts with 3, one that
+    brings a single token at position 200) and on single tokens around page borders and window edges, against the plain
+    attention: folded queries for the mixed scores, unequal key and value sizes, window, sink, gate and factor."""
+    from rusty_llama_b200.kernels import ops
+
+    rng = np.random.default_rng(H * 7 + kd)
+    dt = torch.bfloat16
+    lens = [(70, 100), (0, 3), (200, 1)]
+    n_pages, width = 12, 4
+    perm = rng.permutation(n_pages)
+    table = np.zeros((3, width), dtype=np.int32)
+    kp = torch.full((n_pages, G, 64, kd), 2.0, dtype=dt, device="cuda")
+    vp = torch.full((n_pages, G, 64, vd), -2.0, dtype=dt, device="cuda")
+    mix = (np.eye(H) * 0.8 + 0.4 * rng.standard_normal((H, H))).astype(np.float32).astype(np.float64) if talk else None
+    sink = 1.5 * rng.standard_normal(H) if use_sink else None
+    scale = 1.3 / np.sqrt(kd)
+    ks, vs, qs, refs, at = [], [], [], [], 0
+    for s, (held, n) in enumerate(lens):
+        L = held + n
+        k = _rounded(rng.standard_normal((L, G, kd)), dt)
+        v = _rounded(rng.standard_normal((L, G, vd)), dt)
+        q = _rounded(rng.standard_normal((L, H, kd)), dt)
+        for i in range((L + 63) // 64):
+            table[s, i] = perm[at]
+            m = min(64, L - 64 * i)
+            kp[perm[at], :, :m] = _dev(k[64 * i : 64 * i + m], dt).transpose(0, 1)
+            vp[perm[at], :, :m] = _dev(v[64 * i : 64 * i + m], dt).transpose(0, 1)
+            at += 1
+        refs.append(pr.softmax_attention(q, k, v, scale, window, sink, mix)[held:])
+        qs.append(q[held:])
+        ks.append(k)
+        vs.append(v)
+    T = sum(n for _, n in lens)
+    q_t = _dev(np.concatenate(qs).reshape(T, H * kd), dt)
+    gate = _rounded(rng.standard_normal((T, H * vd)), dt)
+    ref = np.concatenate(refs) * pr.sigmoid(gate) * 0.6
+    start = _i32(np.concatenate([[0], np.cumsum([n for _, n in lens])]))
+    pos0 = _i32([h for h, _ in lens])
+    qq = ops.fold_queries(q_t, _dev(mix, torch.float32), H, G, kd) if talk else q_t
+    wide = torch.zeros((T, H * vd + 6), dtype=dt, device="cuda")
+    out = ops.flash_mix(qq, kp, vp, torch.from_numpy(table).cuda(), start, pos0, 100, H, G, kd, vd, scale, window=window,
+                        sink=None if sink is None else _dev(sink, torch.float32), folded=talk, gate=_dev(gate, dt), out_scale=0.6, out=wide[:, : H * vd])
+    err = np.abs(out.to(torch.float64).cpu().numpy() - ref).max()
+    assert err <= 2.5e-2 * max(1.0, np.abs(ref).max()), err
+    assert float(wide[:, H * vd :].abs().max()) == 0.0
+    # single tokens of the first sequence, as a decode step of one sequence each
+    k, v = ks[0], vs[0]
+    full = pr.softmax_attention(np.concatenate([np.zeros((70, H, kd)), qs[0]]), k, v, scale, window, sink, mix)
+    for p in (70, 127, 128, 129, 169):
+        q1 = _dev(qs[0][p - 70 : p - 69].reshape(1, H * kd), dt)
+        qq = ops.fold_queries(q1, _dev(mix, torch.float32), H, G, kd) if talk else q1
+        out = ops.flash_mix(qq, kp, vp, torch.from_numpy(table[:1]).cuda(), _i32([0, 1]), _i32([p]), 1, H, G, kd, vd, scale, window=window,
+                            sink=None if sink is None else _dev(sink, torch.float32), folded=talk)
+        err = np.abs(out.to(torch.float64).cpu().numpy()[0] - full[p]).max()
+        assert err <= 2.5e-2 * max(1.0, np.abs(full).max()), (p, err)
