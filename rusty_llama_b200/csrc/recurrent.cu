@@ -128,6 +128,250 @@ RL_API int rl_decay_attn(const void* q, const void* k, const void* v, int dtype,
   RL_LAUNCH_RESULT();
 }
 
+// ---------------------------------------------------------------- the same recurrence, chunk by chunk
+// For prompts.  A sequence's tokens are cut into chunks of DC; with n tokens in a chunk, S the state before it, lam the decay:
+//   U      = sum_i lam^(n-1-i) k_i v_i^T                                   (1) what the chunk adds to the state, every chunk at once
+//   S_next = lam^n S + U                                                    (2) the states before every chunk, chunk after chunk
+//   o_i    = lam^(i+1) S^T q_i + sum_{j<=i} lam^(i-j) (q_i . k_j) v_j       (3) the outputs, every chunk at once
+// Three kernels over a scratch of one [dim, vdim] matrix per (sequence, head, chunk).  All of it is 32-bit FMA arithmetic;
+// only powers of lam with exponents >= 0 occur.  The order of the sums differs from the token-by-token kernel's and depends
+// on where the chunks fall, so runs that promise equal bits for every cut of a sequence keep to the other kernel.
+#define DC 64       // tokens per chunk
+#define DC_COLS 64  // state columns per block
+
+// (1): grid (S * H, chunks, column tiles), 256 threads: thread (ty, tx) owns rows ty + 16 a and columns 4 tx .. 4 tx + 3.
+template <typename T>
+__global__ void __launch_bounds__(256)
+decay_chunk_state_kernel(const T* __restrict__ k, const T* __restrict__ v, int in_stride, const float* __restrict__ decay,
+                         const int* __restrict__ seq_start, float* __restrict__ scratch, int max_chunks, int H, int dim, int vdim, int act) {
+  extern __shared__ float sm[];
+  const int s = blockIdx.x / H, h = blockIdx.x % H, c = blockIdx.y, col0 = blockIdx.z * DC_COLS;
+  const int t0 = seq_start[s] + c * DC;
+  const int n = min(DC, seq_start[s + 1] - t0);
+  if (n <= 0) return;
+  float* k_s = sm;             // [DC][dim], weighted by lam^(n-1-i)
+  float* v_s = sm + DC * dim;  // [DC][DC_COLS]
+  const float lam = decay[h];
+  for (int idx = threadIdx.x; idx < n * dim; idx += 256) {
+    const int i = idx / dim, r = idx - i * dim;
+    float kv = to_f32(k[(size_t)(t0 + i) * in_stride + (size_t)h * dim + r]);
+    if (act) kv = silu_f(kv);
+    k_s[idx] = kv * powf(lam, (float)(n - 1 - i));
+  }
+  for (int idx = threadIdx.x; idx < n * DC_COLS; idx += 256) {
+    const int i = idx / DC_COLS, cc = idx - i * DC_COLS;
+    float vv = 0.f;
+    if (col0 + cc < vdim) {
+      vv = to_f32(v[(size_t)(t0 + i) * in_stride + (size_t)h * vdim + col0 + cc]);
+      if (act) vv = silu_f(vv);
+    }
+    v_s[idx] = vv;
+  }
+  __syncthreads();
+  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+  float acc[16][4];
+#pragma unroll
+  for (int a = 0; a < 16; ++a) acc[a][0] = acc[a][1] = acc[a][2] = acc[a][3] = 0.f;
+  for (int i = 0; i < n; ++i) {
+    const float4 vv = *reinterpret_cast<const float4*>(v_s + i * DC_COLS + 4 * tx);
+#pragma unroll
+    for (int a = 0; a < 16; ++a) {
+      const int r = ty + 16 * a;
+      if (r < dim) {
+        const float kv = k_s[i * dim + r];
+        acc[a][0] += kv * vv.x;
+        acc[a][1] += kv * vv.y;
+        acc[a][2] += kv * vv.z;
+        acc[a][3] += kv * vv.w;
+      }
+    }
+  }
+  float* u = scratch + ((size_t)blockIdx.x * max_chunks + c) * dim * vdim;
+#pragma unroll
+  for (int a = 0; a < 16; ++a) {
+    const int r = ty + 16 * a;
+    if (r < dim) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int col = col0 + 4 * tx + e;
+        if (col < vdim) u[(size_t)r * vdim + col] = acc[a][e];
+      }
+    }
+  }
+}
+
+// (2): one thread per element of a (sequence, head)'s state; leaves in every chunk's place the state BEFORE that chunk.
+__global__ void decay_chunk_scan_kernel(const float* __restrict__ decay, float* __restrict__ state, const int* __restrict__ slot_ids,
+                                        const int* __restrict__ seq_start, float* __restrict__ scratch, int max_chunks, int H, int elems) {
+  const int s = blockIdx.x / H, h = blockIdx.x % H;
+  const int e = blockIdx.y * blockDim.x + threadIdx.x;
+  if (e >= elems) return;
+  const int len = seq_start[s + 1] - seq_start[s];
+  const float lam = decay[h];
+  float* st = state + ((size_t)slot_ids[s] * H + h) * elems + e;
+  float* u = scratch + (size_t)blockIdx.x * max_chunks * elems + e;
+  float S = *st;
+  const float lam_full = powf(lam, (float)DC);
+  for (int c = 0; c * DC < len; ++c) {
+    const int n = min(DC, len - c * DC);
+    const float add = u[(size_t)c * elems];
+    u[(size_t)c * elems] = S;
+    S = (n == DC ? lam_full : powf(lam, (float)n)) * S + add;
+  }
+  *st = S;
+}
+
+// (3): grid as (1).  Thread (ty, tx): scores P[ty + 16 a][tx + 16 b], then outputs for rows ty + 16 a and columns 4 tx .. 4 tx + 3.
+template <typename T>
+__global__ void __launch_bounds__(256)
+decay_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int in_stride,
+                       const float* __restrict__ decay, const int* __restrict__ seq_start, const float* __restrict__ scratch,
+                       int max_chunks, float* __restrict__ out, int out_stride, int H, int dim, int vdim, int act) {
+  extern __shared__ float sm[];
+  const int s = blockIdx.x / H, h = blockIdx.x % H, c = blockIdx.y, col0 = blockIdx.z * DC_COLS;
+  const int t0 = seq_start[s] + c * DC;
+  const int n = min(DC, seq_start[s + 1] - t0);
+  if (n <= 0) return;
+  const int DS = dim + 1;  // rows one apart in the banks
+  float* q_s = sm;                    // [DC][DS]
+  float* k_s = q_s + DC * DS;         // [DC][DS]
+  float* v_s = k_s + DC * DS;         // [DC][DC_COLS]
+  float* p_s = v_s + DC * DC_COLS;    // [DC][DC + 1]
+  float* pw = p_s + DC * (DC + 1);    // lam^0 .. lam^DC
+  const float lam = decay[h];
+  for (int i = threadIdx.x; i <= DC; i += 256) pw[i] = powf(lam, (float)i);
+  for (int idx = threadIdx.x; idx < DC * dim; idx += 256) {
+    const int i = idx / dim, r = idx - i * dim;
+    float qv = 0.f, kv = 0.f;
+    if (i < n) {
+      const size_t at = (size_t)(t0 + i) * in_stride + (size_t)h * dim + r;
+      qv = to_f32(q[at]);
+      kv = to_f32(k[at]);
+      if (act) {
+        qv = silu_f(qv);
+        kv = silu_f(kv);
+      }
+    }
+    q_s[i * DS + r] = qv;
+    k_s[i * DS + r] = kv;
+  }
+  for (int idx = threadIdx.x; idx < DC * DC_COLS; idx += 256) {
+    const int i = idx / DC_COLS, cc = idx - i * DC_COLS;
+    float vv = 0.f;
+    if (i < n && col0 + cc < vdim) {
+      vv = to_f32(v[(size_t)(t0 + i) * in_stride + (size_t)h * vdim + col0 + cc]);
+      if (act) vv = silu_f(vv);
+    }
+    v_s[idx] = vv;
+  }
+  __syncthreads();
+  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+  {
+    float p[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a) p[a][0] = p[a][1] = p[a][2] = p[a][3] = 0.f;
+    for (int r = 0; r < dim; ++r) {
+      float qa[4], kb[4];
+#pragma unroll
+      for (int a = 0; a < 4; ++a) qa[a] = q_s[(ty + 16 * a) * DS + r];
+#pragma unroll
+      for (int b = 0; b < 4; ++b) kb[b] = k_s[(tx + 16 * b) * DS + r];
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) p[a][b] += qa[a] * kb[b];
+    }
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const int i = ty + 16 * a, j = tx + 16 * b;
+        p_s[i * (DC + 1) + j] = j <= i ? p[a][b] * pw[i - j] : 0.f;
+      }
+  }
+  __syncthreads();
+  float intra[4][4], inter[4][4];
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) intra[a][e] = inter[a][e] = 0.f;
+  for (int j = 0; j < n; ++j) {
+    const float4 vv = *reinterpret_cast<const float4*>(v_s + j * DC_COLS + 4 * tx);
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+      const float pv = p_s[(ty + 16 * a) * (DC + 1) + j];
+      intra[a][0] += pv * vv.x;
+      intra[a][1] += pv * vv.y;
+      intra[a][2] += pv * vv.z;
+      intra[a][3] += pv * vv.w;
+    }
+  }
+  const float* sp = scratch + ((size_t)blockIdx.x * max_chunks + c) * dim * vdim;  // the state before this chunk
+  const bool vec = (vdim % 4 == 0) && (col0 + 4 * tx + 3 < vdim);
+  for (int r = 0; r < dim; ++r) {
+    float sv[4];
+    if (vec) {
+      const float4 t = *reinterpret_cast<const float4*>(sp + (size_t)r * vdim + col0 + 4 * tx);
+      sv[0] = t.x; sv[1] = t.y; sv[2] = t.z; sv[3] = t.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sv[e] = (col0 + 4 * tx + e < vdim) ? sp[(size_t)r * vdim + col0 + 4 * tx + e] : 0.f;
+    }
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+      const float qv = q_s[(ty + 16 * a) * DS + r];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) inter[a][e] += qv * sv[e];
+    }
+  }
+#pragma unroll
+  for (int a = 0; a < 4; ++a) {
+    const int i = ty + 16 * a;
+    if (i < n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int col = col0 + 4 * tx + e;
+        if (col < vdim) out[(size_t)(t0 + i) * out_stride + (size_t)h * vdim + col] = intra[a][e] + pw[i + 1] * inter[a][e];
+      }
+    }
+  }
+}
+
+RL_API long long rl_decay_attn_chunked_scratch_floats(int n_seqs, int max_q_len, int H, int dim, int vdim) {
+  return (long long)n_seqs * H * ((max_q_len + DC - 1) / DC) * dim * vdim;
+}
+
+RL_API int rl_decay_attn_chunked(const void* q, const void* k, const void* v, int dtype, int in_stride, const float* decay, float* state,
+                                 const int* slot_ids, const int* seq_start, float* scratch, float* out, int out_stride, int n_seqs,
+                                 int max_q_len, int H, int dim, int vdim, int act, cudaStream_t stream) {
+  if (n_seqs <= 0 || max_q_len <= 0 || H <= 0 || dim <= 0 || vdim <= 0 || !scratch)
+    RL_REFUSE(1, "decay_attn_chunked: S=%d max_q=%d H=%d dim=%d vdim=%d", n_seqs, max_q_len, H, dim, vdim);
+  if (dim > 256) RL_REFUSE(2, "decay_attn_chunked: key size %d exceeds 256", dim);
+  const int max_chunks = (max_q_len + DC - 1) / DC, col_tiles = (vdim + DC_COLS - 1) / DC_COLS;
+  if (max_chunks > 65535 || col_tiles > 65535) RL_REFUSE(3, "decay_attn_chunked: %d chunks or %d column tiles exceed the grid", max_chunks, col_tiles);
+  dim3 grid(n_seqs * H, max_chunks, col_tiles);
+  const size_t smem1 = ((size_t)DC * dim + DC * DC_COLS) * sizeof(float);
+  const size_t smem3 = ((size_t)2 * DC * (dim + 1) + DC * DC_COLS + DC * (DC + 1) + DC + 1) * sizeof(float);
+  const int elems = dim * vdim;
+  dim3 grid2(n_seqs * H, (elems + 255) / 256);
+#define RL_DAC(T)                                                                                                                     \
+  do {                                                                                                                                \
+    if (cudaFuncSetAttribute(decay_chunk_state_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1) != cudaSuccess ||  \
+        cudaFuncSetAttribute(decay_chunk_out_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3) != cudaSuccess)      \
+      RL_REFUSE(4, "decay_attn_chunked: %zu bytes of shared memory refused", smem3);                                                 \
+    decay_chunk_state_kernel<T><<<grid, 256, smem1, stream>>>((const T*)k, (const T*)v, in_stride, decay, seq_start, scratch, max_chunks, \
+                                                              H, dim, vdim, act);                                                     \
+    decay_chunk_scan_kernel<<<grid2, 256, 0, stream>>>(decay, state, slot_ids, seq_start, scratch, max_chunks, H, elems);               \
+    decay_chunk_out_kernel<T><<<grid, 256, smem3, stream>>>((const T*)q, (const T*)k, (const T*)v, in_stride, decay, seq_start, scratch,  \
+                                                            max_chunks, out, out_stride, H, dim, vdim, act);                          \
+  } while (0)
+  if (dtype == RL_BF16) RL_DAC(bf16);
+  else if (dtype == RL_F32) RL_DAC(float);
+  else RL_REFUSE(5, "decay_attn_chunked: unknown dtype %d", dtype);
+#undef RL_DAC
+  RL_LAUNCH_RESULT();
+}
+
 // ---------------------------------------------------------------- norm of a 32-bit row, weight, gate
 template <typename T, typename TW>
 __global__ void rms_gate_kernel(const float* __restrict__ x, int x_stride, const TW* __restrict__ w, float eps, const T* __restrict__ gate,
@@ -202,10 +446,99 @@ __global__ void min_gru_kernel(const T* __restrict__ z, const T* __restrict__ x,
   *st = S;
 }
 
+// The same for long prompts: a sequence's tokens are cut into GRU_SEGS stretches, one per warp.  Each warp first runs its stretch
+// from a zero state, which gives the stretch as a map S -> A S + B; the maps before a stretch, applied in order to the sequence's
+// state, give the state it starts from; a second run through the stretch writes the results.  (The sums come out in another
+// order than in the token-by-token kernel, and the order depends on where the stretches fall.)
+#define GRU_SEGS 16
+
+template <typename T>
+__global__ void __launch_bounds__(32 * GRU_SEGS)
+min_gru_seg_kernel(const T* __restrict__ z, const T* __restrict__ x, const T* __restrict__ g, int in_stride, const float* __restrict__ z_bias,
+                   const float* __restrict__ x_bias, float* __restrict__ state, const int* __restrict__ slot_ids,
+                   const int* __restrict__ seq_start, float out_scale, T* __restrict__ out, int out_stride, int width) {
+  __shared__ float A_s[GRU_SEGS][32], B_s[GRU_SEGS][32];
+  const int lane = threadIdx.x, w = threadIdx.y;
+  const int s = blockIdx.x, c = blockIdx.y * 32 + lane;
+  const bool ok = c < width;
+  const int t0 = seq_start[s], t1 = seq_start[s + 1];
+  const int seg = (t1 - t0 + GRU_SEGS - 1) / GRU_SEGS;
+  const int a = min(t1, t0 + w * seg), b = min(t1, a + seg);
+  const float bz = (ok && z_bias) ? z_bias[c] : 0.f, bx = (ok && x_bias) ? x_bias[c] : 0.f;
+  float A = 1.f, B = 0.f;
+  if (ok) {
+    for (int base = a; base < b; base += 4) {
+      float zv[4], xv[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (base + j < b) {
+          const size_t at = (size_t)(base + j) * in_stride + c;
+          zv[j] = to_f32(z[at]);
+          xv[j] = to_f32(x[at]);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (base + j < b) {
+          const float zz = logistic(zv[j] + bz);
+          const float u = xv[j] + bx;
+          const float cand = u >= 0.f ? u + 0.5f : logistic(u);
+          B = (1.0f - zz) * B + zz * cand;
+          A *= 1.0f - zz;
+        }
+      }
+    }
+  }
+  A_s[w][lane] = A;
+  B_s[w][lane] = B;
+  __syncthreads();
+  if (!ok) return;
+  float* st = state + (size_t)slot_ids[s] * width + c;
+  float S = *st;
+  for (int j = 0; j < w; ++j) S = A_s[j][lane] * S + B_s[j][lane];
+  for (int base = a; base < b; base += 4) {
+    float zv[4], xv[4], gv[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (base + j < b) {
+        const size_t at = (size_t)(base + j) * in_stride + c;
+        zv[j] = to_f32(z[at]);
+        xv[j] = to_f32(x[at]);
+        gv[j] = to_f32(g[at]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (base + j < b) {
+        const float zz = logistic(zv[j] + bz);
+        const float u = xv[j] + bx;
+        const float cand = u >= 0.f ? u + 0.5f : logistic(u);
+        S = (1.0f - zz) * S + zz * cand;
+        out[(size_t)(base + j) * out_stride + c] = from_f32<T>(S * silu_f(gv[j]) * out_scale);
+      }
+    }
+  }
+  if (w == GRU_SEGS - 1) *st = S;
+}
+
+// max_q_len: the most tokens that a sequence of the step brings if the caller allows the stretch-wise kernel for long sequences
+// (results then depend on how a sequence was cut into steps, within rounding); 0: token by token, the same bits for every cut.
 RL_API int rl_min_gru(const void* z, const void* x, const void* g, int dtype, int in_stride, const float* z_bias, const float* x_bias,
                       float* state, const int* slot_ids, const int* seq_start, float out_scale, void* out, int out_stride, int n_seqs,
-                      int width, cudaStream_t stream) {
+                      int width, int max_q_len, cudaStream_t stream) {
   if (n_seqs <= 0 || width <= 0 || !z || !x || !g || !state || !out) RL_REFUSE(1, "min_gru: S=%d width=%d", n_seqs, width);
+  if (max_q_len >= 8 * GRU_SEGS) {
+    dim3 grid(n_seqs, (width + 31) / 32), block(32, GRU_SEGS);
+    if (dtype == RL_BF16)
+      min_gru_seg_kernel<bf16><<<grid, block, 0, stream>>>((const bf16*)z, (const bf16*)x, (const bf16*)g, in_stride, z_bias, x_bias, state,
+                                                           slot_ids, seq_start, out_scale, (bf16*)out, out_stride, width);
+    else if (dtype == RL_F32)
+      min_gru_seg_kernel<float><<<grid, block, 0, stream>>>((const float*)z, (const float*)x, (const float*)g, in_stride, z_bias, x_bias,
+                                                            state, slot_ids, seq_start, out_scale, (float*)out, out_stride, width);
+    else
+      RL_REFUSE(2, "min_gru: unknown dtype %d", dtype);
+    RL_LAUNCH_RESULT();
+  }
   const int th = width >= 128 ? 128 : ((width + 31) / 32) * 32;
   dim3 grid(n_seqs, (width + th - 1) / th);
   if (dtype == RL_BF16)

@@ -1326,11 +1326,24 @@ def attn_ext(
 
 
 # ------------------------------------------------------------------ recurrent mixers (csrc/recurrent.cu)
+DECAY_CHUNK = 64  # tokens per chunk of the chunked kernels
+DECAY_CHUNKED_MAX_DIM = 256
+
+
+def decay_attn_chunked_scratch_floats(n_seqs: int, max_q_len: int, num_heads: int, dim: int, vdim: int) -> int:
+    return n_seqs * num_heads * ((max_q_len + DECAY_CHUNK - 1) // DECAY_CHUNK) * dim * vdim
+
+
 def decay_attn(
     q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, slot_ids: torch.Tensor,
     seq_start: torch.Tensor, num_heads: int, dim: int, vdim: int, silu: bool = False, out: Optional[torch.Tensor] = None,
+    max_q_len: int = 0, scratch: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """Linear attention with a decay per head, S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t, through the sequences' states.
+
+    max_q_len, scratch: 0 / None = token by token (equal bits for every cut of a sequence).  With the most tokens that a sequence
+    of the step brings and a float32 scratch of `decay_attn_chunked_scratch_floats(...)`, the sequences are worked chunk by chunk,
+    all chunks side by side (equal within rounding; key sizes up to 256).
 
     q, k: [T, H dim], v: [T, H vdim], views of one projection's rows (equal row strides).  decay: float32 [H].
     state: float32 [slots, H, dim, vdim]; sequence i of the step owns state[slot_ids[i]] and the tokens seq_start[i] .. seq_start[i+1].
@@ -1352,6 +1365,16 @@ def decay_attn(
     _cuda(out, "decay_attn out", torch.float32)
     _need(tuple(out.shape) == (T, num_heads * vdim), "decay_attn: out has the wrong shape")
     lib = build.load("recurrent")
+    if max_q_len > 0 and scratch is not None:
+        _cuda(scratch, "decay_attn scratch", torch.float32)
+        _need(dim <= DECAY_CHUNKED_MAX_DIM, f"decay_attn: the chunked kernels take key sizes up to {DECAY_CHUNKED_MAX_DIM}")
+        _need(scratch.numel() >= decay_attn_chunked_scratch_floats(S, max_q_len, num_heads, dim, vdim), "decay_attn: scratch too small")
+        rc = lib.rl_decay_attn_chunked(
+            _p(q), _p(k), _p(v), c_int(_dt(q, "decay_attn")), c_int(q.stride(0)), _p(decay), _p(state), _p(slot_ids), _p(seq_start), _p(scratch),
+            _p(out), c_int(out.stride(0)), c_int(S), c_int(max_q_len), c_int(num_heads), c_int(dim), c_int(vdim), c_int(1 if silu else 0), _stream(),
+        )
+        _check(lib, rc, "decay_attn_chunked", kernels=3)
+        return out
     rc = lib.rl_decay_attn(
         _p(q), _p(k), _p(v), c_int(_dt(q, "decay_attn")), c_int(q.stride(0)), _p(decay), _p(state), _p(slot_ids), _p(seq_start), _p(out),
         c_int(out.stride(0)), c_int(S), c_int(num_heads), c_int(dim), c_int(vdim), c_int(1 if silu else 0), _stream(),
@@ -1391,10 +1414,13 @@ def rms_gate(
 
 def min_gru(
     z: torch.Tensor, x: torch.Tensor, g: torch.Tensor, z_bias: Optional[torch.Tensor], x_bias: Optional[torch.Tensor], state: torch.Tensor,
-    slot_ids: torch.Tensor, seq_start: torch.Tensor, out_scale: float = 1.0, out: Optional[torch.Tensor] = None,
+    slot_ids: torch.Tensor, seq_start: torch.Tensor, out_scale: float = 1.0, out: Optional[torch.Tensor] = None, max_q_len: int = 0,
 ) -> torch.Tensor:
     """Element by element S_t = (1 - z_t) S_(t-1) + z_t c_t with z_t = sigmoid(z + z_bias), u = x + x_bias,
     c = u + 1/2 where u >= 0 else sigmoid(u); returns S_t * silu(g) * out_scale in the inputs' type.
+
+    max_q_len: 0 = token by token (equal bits for every cut of a sequence); the most tokens a sequence of the step brings = long
+    sequences are cut into stretches that run side by side (equal within rounding).
 
     z, x, g: [T, width] views of one projection's rows (equal row strides).  state: float32 [slots, width]."""
     T, width = z.shape
@@ -1418,7 +1444,7 @@ def min_gru(
     lib = build.load("recurrent")
     rc = lib.rl_min_gru(
         _p(z), _p(x), _p(g), c_int(_dt(z, "min_gru")), c_int(z.stride(0)), _p(z_bias), _p(x_bias), _p(state), _p(slot_ids), _p(seq_start),
-        c_float(out_scale), _p(out), c_int(out.stride(0)), c_int(S), c_int(width), _stream(),
+        c_float(out_scale), _p(out), c_int(out.stride(0)), c_int(S), c_int(width), c_int(max_q_len), _stream(),
     )
     _check(lib, rc, "min_gru")
     return out

@@ -17,6 +17,10 @@ from ..kernels.linear import linear, linear_to_stream
 from .base import MIXERS, Mixer, ParamInfo, StateNeed
 
 
+# prompt steps whose longest sequence brings fewer tokens than this go token by token like a decode step
+_CHUNKED_MIN_TOKENS = 32
+
+
 @MIXERS.register("decay_linear_attention")
 class DecayLinearAttention(Mixer):
     """Linear attention with a constant decay per head:
@@ -94,7 +98,17 @@ class DecayLinearAttention(Mixer):
         q, k = proj[:, : self.qd], proj[:, self.qd : 2 * self.qd]
         v = proj[:, 2 * self.qd : 2 * self.qd + self.vd]
         gate = proj[:, 2 * self.qd + self.vd :] if self.has_gate else None
-        o = ops.decay_attn(q, k, v, self.decay, cache.state, step.slot_ids, step.seq_start, self.H, self.dim, self.vdim, silu=self.silu)
+        # a prompt step of a bfloat16 run works its sequences chunk by chunk, all chunks at once; 32-bit runs and single
+        # tokens go token by token (the same bits however a sequence is cut into steps)
+        chunked = xn.dtype == torch.bfloat16 and step.max_q_len >= _CHUNKED_MIN_TOKENS and self.dim <= ops.DECAY_CHUNKED_MAX_DIM
+        scratch = None
+        if chunked:
+            need = ops.decay_attn_chunked_scratch_floats(step.n_seqs, step.max_q_len, self.H, self.dim, self.vdim)
+            scratch = self.rt.workspace.get("decay_attn_chunks", need, torch.float32)
+        o = ops.decay_attn(
+            q, k, v, self.decay, cache.state, step.slot_ids, step.seq_start, self.H, self.dim, self.vdim, silu=self.silu,
+            max_q_len=step.max_q_len if chunked else 0, scratch=scratch,
+        )
         a = ops.rms_gate(o, self.w_norm, self.eps, gate, xn.dtype, out_scale=self.out_scale, out=out)
         return a, self.w_o
 
@@ -156,6 +170,6 @@ class MinGRU(Mixer):
         w = self.width
         a = ops.min_gru(
             proj[:, :w], proj[:, w : 2 * w], proj[:, 2 * w :], self.b_z, self.b_x, cache.state, step.slot_ids, step.seq_start,
-            out_scale=self.out_scale, out=out,
+            out_scale=self.out_scale, out=out, max_q_len=step.max_q_len if xn.dtype == torch.bfloat16 else 0,
         )
         return a, self.w_o

@@ -641,3 +641,66 @@ def test_tensor_core_attention_with_options(H, G, kd, vd, window, talk, use_sink
                             sink=None if sink is None else _dev(sink, torch.float32), folded=talk)
         err = np.abs(out.to(torch.float64).cpu().numpy()[0] - full[p]).max()
         assert err <= 2.5e-2 * max(1.0, np.abs(full).max()), (p, err)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H, dim, vdim", [(2, 24, 40), (1, 72, 8), (2, 128, 64), (1, 256, 200)])
+def test_chunked_decay_attention_on_a_ragged_step(dtype, H, dim, vdim):
+    """The chunk-by-chunk kernels on a step of four sequences of 163 (going on from a state that 37 tokens have left), 64, 65
+    and 1 tokens, against the plain recurrence; the states they leave must be those the token-by-token kernel leaves."""
+    from rusty_llama_b200.kernels import ops
+
+    rng = np.random.default_rng(dim + vdim)
+    decay = np.array([0.6, 0.999][:H], dtype=np.float32).astype(np.float64)
+    lens = [200, 64, 65, 1]
+    raw = [_rounded(rng.standard_normal((L, H * (2 * dim + vdim))), dtype) for L in lens]
+
+    def split(x):
+        return x[:, : H * dim], x[:, H * dim : 2 * H * dim], x[:, 2 * H * dim :]
+
+    ref = []
+    for x in raw:
+        q, k, v = (pr.silu(t) for t in split(x))
+        ref.append(pr.decayed_linear_attention(q.reshape(-1, H, dim), k.reshape(-1, H, dim), v.reshape(-1, H, vdim), decay).reshape(-1, H * vdim))
+    dec = _dev(decay, torch.float32)
+    states = {}
+    for how in ("chunked", "plain"):
+        state = torch.zeros((5, H, dim, vdim), dtype=torch.float32, device="cuda")
+        q, k, v = split(_dev(raw[0][:37], dtype))
+        ops.decay_attn(q, k, v, dec, state, _i32([3]), _i32([0, 37]), H, dim, vdim, silu=True)
+        x = _dev(np.concatenate([raw[0][37:], raw[1], raw[2], raw[3]]), dtype)
+        q, k, v = split(x)
+        starts = _i32(np.concatenate([[0], np.cumsum([163, 64, 65, 1])]))
+        kw = {}
+        if how == "chunked":
+            kw = dict(max_q_len=163, scratch=torch.full((ops.decay_attn_chunked_scratch_floats(4, 163, H, dim, vdim),), float("nan"), device="cuda"))
+        out = ops.decay_attn(q, k, v, dec, state, _i32([3, 0, 4, 1]), starts, H, dim, vdim, silu=True, **kw).to(torch.float64).cpu().numpy()
+        want = np.concatenate([ref[0][37:], ref[1], ref[2], ref[3]])
+        assert np.abs(out - want).max() <= 5e-5 * max(1.0, np.abs(want).max()), how
+        states[how] = state.cpu().numpy()
+    assert np.abs(states["chunked"] - states["plain"]).max() <= 5e-5 * max(1.0, np.abs(states["plain"]).max())
+    assert np.abs(states["chunked"][2]).max() == 0.0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [7, 96, 300])
+def test_min_gru_in_stretches(dtype, width):
+    """Sequences of 263 (going on from a state that 37 tokens have left), 129 and 5 tokens in one step, cut into stretches that
+    run side by side, against the plain recurrence."""
+    from rusty_llama_b200.kernels import ops
+
+    rng = np.random.default_rng(width + 1)
+    lens = [300, 129, 5]
+    raw = [_rounded(2.0 * rng.standard_normal((L, 3 * width)), dtype) for L in lens]
+    bz = rng.standard_normal(width).astype(np.float32).astype(np.float64)
+    bx = rng.standard_normal(width).astype(np.float32).astype(np.float64)
+    ref = [pr.min_gru(pr.sigmoid(x[:, :width] + bz), x[:, width : 2 * width] + bx) * pr.silu(x[:, 2 * width :]) for x in raw]
+    state = torch.zeros((4, width), dtype=torch.float32, device="cuda")
+    args = (_dev(bz, torch.float32), _dev(bx, torch.float32), state)
+    x = _dev(raw[0][:37], dtype)
+    ops.min_gru(x[:, :width], x[:, width : 2 * width], x[:, 2 * width :], *args, _i32([2]), _i32([0, 37]))
+    x = _dev(np.concatenate([raw[0][37:], raw[1], raw[2]]), dtype)
+    out = ops.min_gru(x[:, :width], x[:, width : 2 * width], x[:, 2 * width :], *args, _i32([2, 0, 3]), _i32([0, 263, 392, 397]), max_q_len=263)
+    want = np.concatenate([ref[0][37:], ref[1], ref[2]])
+    assert np.abs(out.to(torch.float64).cpu().numpy() - want).max() <= _tol(dtype, 2e-5, 1.5e-2) * max(1.0, np.abs(want).max())
+    assert float(state[1].abs().max()) == 0.0
