@@ -56,23 +56,38 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 // ---------------------------------------------------------------- folded queries
 // out[t][h][c][i] = sum over the heads g of kv head c of mix[h][g] * q[t][g][i], in 32-bit, stored as bfloat16.
-__global__ void fold_queries_kernel(const bf16* __restrict__ q, int q_stride, const float* __restrict__ mix, bf16* __restrict__ out, int H,
-                                    int K, int kdim) {
+// One block per token: the token's rotated queries (32-bit) and the mixing matrix in shared memory; a warp makes one
+// (head, kv head) part at a time, its lanes the dimensions.
+__global__ void __launch_bounds__(256)
+fold_queries_kernel(const bf16* __restrict__ q, int q_stride, const float* __restrict__ mix, bf16* __restrict__ out, int H, int K, int kdim) {
+  extern __shared__ float fq_s[];  // q [H][kdim], mix [H][H]
+  float* q_s = fq_s;
+  float* m_s = fq_s + H * kdim;
   const int t = blockIdx.x, rep = H / K;
   const bf16* row = q + (size_t)t * q_stride;
+  for (int i = threadIdx.x; i < H * kdim; i += blockDim.x) q_s[i] = __bfloat162float(row[i]);
+  for (int i = threadIdx.x; i < H * H; i += blockDim.x) m_s[i] = mix[i];
+  __syncthreads();
   bf16* o = out + (size_t)t * H * K * kdim;
-  for (int idx = threadIdx.x; idx < H * K * kdim; idx += blockDim.x) {
-    const int i = idx % kdim, c = (idx / kdim) % K, h = idx / (kdim * K);
-    float acc = 0.f;
-    for (int g = c * rep; g < (c + 1) * rep; ++g) acc += mix[h * H + g] * __bfloat162float(row[(size_t)g * kdim + i]);
-    o[idx] = __float2bfloat16_rn(acc);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int hc = warp; hc < H * K; hc += nw) {
+    const int h = hc / K, c = hc - h * K;
+    const float* m = m_s + h * H + c * rep;
+    const float* qg = q_s + (size_t)c * rep * kdim;
+    for (int i = lane; i < kdim; i += 32) {
+      float acc = 0.f;
+      for (int g = 0; g < rep; ++g) acc += m[g] * qg[g * kdim + i];
+      o[(size_t)hc * kdim + i] = __float2bfloat16_rn(acc);
+    }
   }
 }
 
 RL_API int rl_fold_queries(const void* q, int q_stride, const float* mix, void* out, int n_tokens, int H, int K, int kdim,
                            cudaStream_t stream) {
   if (n_tokens <= 0 || H <= 0 || K <= 0 || kdim <= 0 || H % K || !q || !mix || !out) RL_REFUSE(1, "fold_queries: T=%d H=%d K=%d kdim=%d", n_tokens, H, K, kdim);
-  fold_queries_kernel<<<n_tokens, 256, 0, stream>>>((const bf16*)q, q_stride, mix, (bf16*)out, H, K, kdim);
+  const size_t smem = ((size_t)H * kdim + (size_t)H * H) * sizeof(float);
+  if (smem > 48 * 1024) RL_REFUSE(2, "fold_queries: %d heads of %d numbers do not fit shared memory", H, kdim);
+  fold_queries_kernel<<<n_tokens, 256, smem, stream>>>((const bf16*)q, q_stride, mix, (bf16*)out, H, K, kdim);
   RL_LAUNCH_RESULT();
 }
 

@@ -450,7 +450,7 @@ __global__ void min_gru_kernel(const T* __restrict__ z, const T* __restrict__ x,
 // from a zero state, which gives the stretch as a map S -> A S + B; the maps before a stretch, applied in order to the sequence's
 // state, give the state it starts from; a second run through the stretch writes the results.  (The sums come out in another
 // order than in the token-by-token kernel, and the order depends on where the stretches fall.)
-#define GRU_SEGS 16
+#define GRU_SEGS 32
 
 template <typename T>
 __global__ void __launch_bounds__(32 * GRU_SEGS)
@@ -467,10 +467,10 @@ min_gru_seg_kernel(const T* __restrict__ z, const T* __restrict__ x, const T* __
   const float bz = (ok && z_bias) ? z_bias[c] : 0.f, bx = (ok && x_bias) ? x_bias[c] : 0.f;
   float A = 1.f, B = 0.f;
   if (ok) {
-    for (int base = a; base < b; base += 4) {
-      float zv[4], xv[4];
+    for (int base = a; base < b; base += 8) {
+      float zv[8], xv[8];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < 8; ++j) {
         if (base + j < b) {
           const size_t at = (size_t)(base + j) * in_stride + c;
           zv[j] = to_f32(z[at]);
@@ -478,7 +478,7 @@ min_gru_seg_kernel(const T* __restrict__ z, const T* __restrict__ x, const T* __
         }
       }
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < 8; ++j) {
         if (base + j < b) {
           const float zz = logistic(zv[j] + bz);
           const float u = xv[j] + bx;
@@ -496,10 +496,10 @@ min_gru_seg_kernel(const T* __restrict__ z, const T* __restrict__ x, const T* __
   float* st = state + (size_t)slot_ids[s] * width + c;
   float S = *st;
   for (int j = 0; j < w; ++j) S = A_s[j][lane] * S + B_s[j][lane];
-  for (int base = a; base < b; base += 4) {
-    float zv[4], xv[4], gv[4];
+  for (int base = a; base < b; base += 8) {
+    float zv[8], xv[8], gv[8];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < 8; ++j) {
       if (base + j < b) {
         const size_t at = (size_t)(base + j) * in_stride + c;
         zv[j] = to_f32(z[at]);
@@ -508,7 +508,7 @@ min_gru_seg_kernel(const T* __restrict__ z, const T* __restrict__ x, const T* __
       }
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < 8; ++j) {
       if (base + j < b) {
         const float zz = logistic(zv[j] + bz);
         const float u = xv[j] + bx;

@@ -86,12 +86,28 @@ def kernel_table(z: dict, T: int, batch: int, ctx: int, peaks: dict) -> Dict[str
         keys_all = sum(min(p + 1, 1 << 30) for p in range(pos0, pos0 + rows // n_seqs)) * n_seqs
         keys_win = sum(min(p + 1, W) for p in range(pos0, pos0 + rows // n_seqs)) * n_seqs
         cache_bytes = lambda keys_per_seq: n_seqs * keys_per_seq * G * 2 * hd * 2  # noqa: E731
-        us = mb._time(lambda i: ops.attn_ext(q, kp, vp, table, seq, pos, H, G, hd, hd, scale, sink=sink), 1, **it)
+        start = torch.arange(n_seqs + 1, dtype=torch.int32, device=dev) * (rows // n_seqs)
+        p0 = torch.full((n_seqs,), pos0, dtype=torch.int32, device=dev)
+        max_q = rows // n_seqs
+        # a plain attention with a sink runs on the plain attention's own kernels
+        if rows > batch:
+            us = mb._time(lambda i: ops.flash_prefill_tc(q, kp, vp, table, start, p0, max_q, H, G, hd, scale=scale, sink=sink), 1, **it)
+        else:
+            from ..parts.attention import decode_splits
+            n_splits = decode_splits(n_seqs, H, G, pos0 + 1, hd)
+            scratch = torch.empty(ops.attn_decode_scratch_floats(n_seqs, H, hd, n_splits), device=dev)
+            lens = torch.full((n_seqs,), pos0 + 1, dtype=torch.int32, device=dev)
+            us = mb._time(lambda i: ops.attn_decode(q, kp, vp, table, lens, H, G, hd, n_splits, scratch, scale=scale, sink=sink), 1, **it)
         note(f"{tag}_attention_sink", us, cache_bytes(pos0 + rows // n_seqs) + rows * H * hd * 4, 4.0 * keys_all * H * hd,
              like=like_prefill if rows > batch else like_decode)
-        if H <= 32:
-            us = mb._time(lambda i: ops.attn_ext(q, kp, vp, table, seq, pos, H, G, hd, hd, scale, window=W, mix=mix, gate=gate), 1, **it)
-            note(f"{tag}_attention_mixed_window_gate", us, cache_bytes(min(W, pos0 + rows // n_seqs)) + rows * H * hd * 6, 4.0 * keys_win * H * hd)
+        if ops.flash_mix_takes(hd, hd, G):
+            us_fold = mb._time(lambda i: ops.fold_queries(q, mix, H, G, hd), 1, **it)
+            note(f"{tag}_fold_queries", us_fold, rows * H * hd * 2 * (1 + G), 2.0 * rows * H * H * hd)
+            qf = ops.fold_queries(q, mix, H, G, hd)
+            us = mb._time(lambda i: ops.flash_mix(qf, kp, vp, table, start, p0, max_q, H, G, hd, hd, scale, window=W, folded=True, gate=gate), 1, **it)
+            # its products: the scores against the keys of all kv heads, and the values
+            note(f"{tag}_attention_mixed_window_gate", us, cache_bytes(min(W, pos0 + rows // n_seqs)) + rows * H * hd * (2 * G + 4), 2.0 * keys_win * H * hd * (G + 1),
+                 like=like_prefill if rows > batch else like_decode)
         # biases, rotation, cache write
         qkv = torch.randn(rows, (H + 2 * G) * hd, device=dev, dtype=bf)
         bias = torch.zeros((H + 2 * G) * hd, device=dev)
@@ -112,7 +128,10 @@ def kernel_table(z: dict, T: int, batch: int, ctx: int, peaks: dict) -> Dict[str
         state = torch.zeros(n_seqs, H, hd, hd, device=dev)
         slots = torch.arange(n_seqs, dtype=torch.int32, device=dev)
         start = torch.arange(n_seqs + 1, dtype=torch.int32, device=dev) * (rows // n_seqs)
-        us = mb._time(lambda i: ops.decay_attn(q, k, v, decay, state, slots, start, H, hd, hd, silu=True), 1, **it)
+        kw = {}
+        if rows > batch:  # a prompt step goes chunk by chunk
+            kw = dict(max_q_len=rows // n_seqs, scratch=torch.empty(ops.decay_attn_chunked_scratch_floats(n_seqs, rows // n_seqs, H, hd, hd), device=dev))
+        us = mb._time(lambda i: ops.decay_attn(q, k, v, decay, state, slots, start, H, hd, hd, silu=True, **kw), 1, **it)
         note(f"{tag}_decay_attention", us, rows * H * hd * (3 * 2 + 4) + 2 * state.numel() * 4, 4.0 * rows * H * hd * hd,
              like=like_prefill if rows > batch else like_decode)
         o = torch.randn(rows, H * hd, device=dev)
@@ -122,7 +141,7 @@ def kernel_table(z: dict, T: int, batch: int, ctx: int, peaks: dict) -> Dict[str
         zx = torch.randn(rows, 3 * gw, device=dev, dtype=bf)
         bz = torch.zeros(gw, device=dev)
         gstate = torch.zeros(n_seqs, gw, device=dev)
-        us = mb._time(lambda i: ops.min_gru(zx[:, :gw], zx[:, gw: 2 * gw], zx[:, 2 * gw:], bz, bz, gstate, slots, start), 1, **it)
+        us = mb._time(lambda i: ops.min_gru(zx[:, :gw], zx[:, gw: 2 * gw], zx[:, 2 * gw:], bz, bz, gstate, slots, start, max_q_len=rows // n_seqs), 1, **it)
         note(f"{tag}_min_gru", us, rows * gw * 8 + 2 * gstate.numel() * 4, 0)
         # the feed-forward's activation (Llama's is fused into its product), the sandwich norm beside Llama's
         hh = torch.randn(rows, ff, device=dev, dtype=bf)
