@@ -8,7 +8,8 @@
 // products of a head's parts c = 0 .. K-1 into one accumulator and goes on as any flash attention does.  Without a mixing
 // matrix a head has one part, its own kv head's keys.
 //
-// A block of four warps owns 64 query rows of one head of one sequence.  A key tile is one cache page.  The loads of a tile
+// A block of four warps owns 64 query rows of one head of one sequence (eight warps and 128 rows for folded queries of a
+// prompt, whose many parts in shared memory leave room for one block per SM only).  A key tile is one cache page.  The loads of a tile
 // are, in order, the keys of each part and then the values; they go through a ring of three buffers with cp.async, two loads
 // ahead of the one in use.  The online softmax (max, sum, rescale) is 32-bit, in base-2 exponents.  Sizes are padded with
 // zeros to HD in shared memory, so key and value sizes in multiples of 8 up to 256 are served.  Prompts and single tokens
@@ -17,9 +18,7 @@
 
 RL_DEFINE_ERROR_TEXT()
 
-#define BM 64   // query rows per block
 #define BN 64   // keys per tile = page size
-#define NTHREADS 128
 #define NBUF 3
 
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem) {
@@ -93,6 +92,7 @@ RL_API int rl_fold_queries(const void* q, int q_stride, const float* mix, void* 
 
 // ---------------------------------------------------------------- the attention
 // Copy rows [n_rows][width] (row stride src_stride) into rows of `stride` elements; width a multiple of 8.
+template <int NTHREADS>
 __device__ __forceinline__ void load_rows(bf16* dst, const bf16* src, size_t src_stride, int n_rows, int width, int stride) {
   const int chunks = width >> 3;
   for (int c = threadIdx.x; c < n_rows * chunks; c += NTHREADS) {
@@ -101,8 +101,8 @@ __device__ __forceinline__ void load_rows(bf16* dst, const bf16* src, size_t src
   }
 }
 
-template <int HD>
-__global__ void __launch_bounds__(NTHREADS)
+template <int HD, int BM>
+__global__ void __launch_bounds__(BM * 2)
 flash_mix_kernel(const bf16* __restrict__ q, long long q_row_stride, int q_head_stride, int parts, const bf16* __restrict__ k_pages,
                  const bf16* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
                  const int* __restrict__ seq_start, const int* __restrict__ seq_pos0, const float* __restrict__ sink,
@@ -110,6 +110,7 @@ flash_mix_kernel(const bf16* __restrict__ q, long long q_row_stride, int q_head_
                  int kdim, int vdim, int window, float scale_log2) {
   constexpr int STRIDE = HD + 8;  // 16 bytes of padding per row keep ldmatrix free of bank conflicts
   constexpr int KSTEPS = HD / 16;
+  constexpr int NTHREADS = BM * 2;  // a warp per 16 query rows
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* ring = reinterpret_cast<bf16*>(smem_raw);  // NBUF x [BN][STRIDE]
   bf16* q_s = ring + NBUF * BN * STRIDE;           // parts x [BM][STRIDE]
@@ -134,7 +135,7 @@ flash_mix_kernel(const bf16* __restrict__ q, long long q_row_stride, int q_head_
   }
   __syncthreads();
   for (int p = 0; p < parts; ++p)
-    load_rows(q_s + (size_t)p * BM * STRIDE, q + (size_t)(tok0 + row0) * q_row_stride + (size_t)h * q_head_stride + (size_t)p * kdim,
+    load_rows<NTHREADS>(q_s + (size_t)p * BM * STRIDE, q + (size_t)(tok0 + row0) * q_row_stride + (size_t)h * q_head_stride + (size_t)p * kdim,
               (size_t)q_row_stride, rows_here, kdim, STRIDE);
   const int* table = block_table + (size_t)s * table_width;
   const int last_pos = pos0 + row0 + rows_here - 1;
@@ -149,9 +150,9 @@ flash_mix_kernel(const bf16* __restrict__ q, long long q_row_stride, int q_head_
     const size_t page = (size_t)table[tile];
     if (part < parts) {
       const int kv = parts > 1 ? part : kh;
-      load_rows(dst, k_pages + ((page * K + kv) * BN) * kdim, (size_t)kdim, BN, kdim, STRIDE);
+      load_rows<NTHREADS>(dst, k_pages + ((page * K + kv) * BN) * kdim, (size_t)kdim, BN, kdim, STRIDE);
     } else {
-      load_rows(dst, v_pages + ((page * K + kh) * BN) * vdim, (size_t)vdim, BN, vdim, STRIDE);
+      load_rows<NTHREADS>(dst, v_pages + ((page * K + kh) * BN) * vdim, (size_t)vdim, BN, vdim, STRIDE);
     }
   };
   issue(0);
@@ -291,9 +292,23 @@ flash_mix_kernel(const bf16* __restrict__ q, long long q_row_stride, int q_head_
   }
 }
 
-RL_API int rl_flash_mix_smem(int hd_max, int parts) {
-  const int HD = hd_max <= 32 ? 32 : (hd_max <= 64 ? 64 : (hd_max <= 128 ? 128 : 256));
-  return (NBUF * BN + parts * BM) * (HD + 8) * (int)sizeof(bf16);
+template <int HD, int BM>
+static int launch_mix_rows(const bf16* q, long long q_row_stride, int q_head_stride, int parts, const bf16* k_pages, const bf16* v_pages,
+                      const int* block_table, int table_width, const int* seq_start, const int* seq_pos0, const float* sink,
+                      const bf16* gate, int gate_stride, float out_scale, bf16* out, int out_stride, int n_seqs, int max_q_len, int H, int K,
+                      int kdim, int vdim, int window, float scale, cudaStream_t stream) {
+  const size_t smem = (size_t)(NBUF * BN + parts * BM) * (HD + 8) * sizeof(bf16);
+  auto kern = flash_mix_kernel<HD, BM>;
+  if (smem > 227 * 1024) RL_REFUSE(8, "flash_mix: %zu bytes of shared memory for %d query parts exceed the SM's", smem, parts);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) RL_REFUSE(8, "flash_mix: cannot get %zu bytes of shared memory", smem);
+  }
+  dim3 grid(H * n_seqs, (max_q_len + BM - 1) / BM);
+  kern<<<grid, BM * 2, smem, stream>>>(q, q_row_stride, q_head_stride, parts, k_pages, v_pages, block_table, table_width, seq_start,
+                                         seq_pos0, sink, gate, gate_stride, out_scale, out, out_stride, H, K, kdim, vdim, window,
+                                         scale * 1.4426950408889634f);
+  RL_LAUNCH_RESULT();
 }
 
 template <int HD>
@@ -301,18 +316,16 @@ static int launch_mix(const bf16* q, long long q_row_stride, int q_head_stride, 
                       const int* block_table, int table_width, const int* seq_start, const int* seq_pos0, const float* sink,
                       const bf16* gate, int gate_stride, float out_scale, bf16* out, int out_stride, int n_seqs, int max_q_len, int H, int K,
                       int kdim, int vdim, int window, float scale, cudaStream_t stream) {
-  const size_t smem = (size_t)(NBUF * BN + parts * BM) * (HD + 8) * sizeof(bf16);
-  auto kern = flash_mix_kernel<HD>;
-  if (smem > 227 * 1024) RL_REFUSE(8, "flash_mix: %zu bytes of shared memory for %d query parts exceed the SM's", smem, parts);
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) RL_REFUSE(8, "flash_mix: cannot get %zu bytes of shared memory", smem);
-  }
-  dim3 grid(H * n_seqs, (max_q_len + BM - 1) / BM);
-  kern<<<grid, NTHREADS, smem, stream>>>(q, q_row_stride, q_head_stride, parts, k_pages, v_pages, block_table, table_width, seq_start,
-                                         seq_pos0, sink, gate, gate_stride, out_scale, out, out_stride, H, K, kdim, vdim, window,
-                                         scale * 1.4426950408889634f);
-  RL_LAUNCH_RESULT();
+  // 128 rows to a block where several query parts would leave one block of 64 rows alone on its SM anyway and the step has
+  // the rows to fill it
+  const size_t smem128 = (size_t)(NBUF * BN + parts * 128) * (HD + 8) * sizeof(bf16);
+  const size_t smem64 = (size_t)(NBUF * BN + parts * 64) * (HD + 8) * sizeof(bf16);
+  if (HD <= 128 && parts > 1 && max_q_len > 64 && smem128 <= 227 * 1024 && 2 * smem64 > 227 * 1024)
+    return launch_mix_rows<HD, 128>(q, q_row_stride, q_head_stride, parts, k_pages, v_pages, block_table, table_width, seq_start, seq_pos0,
+                                    sink, gate, gate_stride, out_scale, out, out_stride, n_seqs, max_q_len, H, K, kdim, vdim, window, scale,
+                                    stream);
+  return launch_mix_rows<HD, 64>(q, q_row_stride, q_head_stride, parts, k_pages, v_pages, block_table, table_width, seq_start, seq_pos0, sink,
+                                 gate, gate_stride, out_scale, out, out_stride, n_seqs, max_q_len, H, K, kdim, vdim, window, scale, stream);
 }
 
 // q: the queries [T][..], row stride q_row_stride, head h at h * q_head_stride, part p of a head at + p * kdim.

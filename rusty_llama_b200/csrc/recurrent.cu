@@ -306,17 +306,18 @@ decay_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ k, const T
       intra[a][3] += pv * vv.w;
     }
   }
-  const float* sp = scratch + ((size_t)blockIdx.x * max_chunks + c) * dim * vdim;  // the state before this chunk
-  const bool vec = (vdim % 4 == 0) && (col0 + 4 * tx + 3 < vdim);
+  // the state before this chunk, this block's columns: through the keys' place in shared memory, which the scores no longer need
+  // (every thread has written its scores, and the barrier above has passed)
+  const float* sp = scratch + ((size_t)blockIdx.x * max_chunks + c) * dim * vdim;
+  float* s_s = k_s;  // [dim][DC_COLS]; DC * (dim + 1) >= dim * DC_COLS
+  for (int idx = threadIdx.x; idx < dim * DC_COLS; idx += 256) {
+    const int r = idx / DC_COLS, cc = idx - r * DC_COLS;
+    s_s[idx] = (col0 + cc < vdim) ? sp[(size_t)r * vdim + col0 + cc] : 0.f;
+  }
+  __syncthreads();
   for (int r = 0; r < dim; ++r) {
-    float sv[4];
-    if (vec) {
-      const float4 t = *reinterpret_cast<const float4*>(sp + (size_t)r * vdim + col0 + 4 * tx);
-      sv[0] = t.x; sv[1] = t.y; sv[2] = t.z; sv[3] = t.w;
-    } else {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) sv[e] = (col0 + 4 * tx + e < vdim) ? sp[(size_t)r * vdim + col0 + 4 * tx + e] : 0.f;
-    }
+    const float4 t = *reinterpret_cast<const float4*>(s_s + r * DC_COLS + 4 * tx);
+    const float sv[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
     for (int a = 0; a < 4; ++a) {
       const float qv = q_s[(ty + 16 * a) * DS + r];

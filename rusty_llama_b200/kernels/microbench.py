@@ -162,6 +162,39 @@ def bench_flash_prefill(a) -> dict:
     return {"kernel": "flash_prefill_tc" if tc else "flash_prefill", "tokens": T, "H": H, "K": K, "hd": hd, "us": round(us, 2), "causal_TFLOPs": round(flops / us / 1e6, 1)}
 
 
+def bench_flash_mix(a) -> dict:
+    """Prompt attention with a window, a gate and scores mixed across heads (folded queries), one sequence of --tokens."""
+    dev = "cuda:0"
+    H, K, hd, T, W = a.heads, a.kv_heads, a.head_dim, a.tokens, a.window
+    ks, vs, table = _paged(1, T, K, hd, 1)
+    q = torch.randn(T, H * hd, device=dev, dtype=torch.bfloat16)
+    gate = torch.randn(T, H * hd, device=dev, dtype=torch.bfloat16)
+    mix = torch.eye(H, device=dev) + 0.1 * torch.randn(H, H, device=dev)
+    seq_start = torch.tensor([0, T], dtype=torch.int32, device=dev)
+    pos0 = torch.zeros(1, dtype=torch.int32, device=dev)
+    qf = ops.fold_queries(q, mix, H, K, hd)
+    us = _time(lambda i: ops.flash_mix(qf, ks[0], vs[0], table, seq_start, pos0, T, H, K, hd, hd, 1.0 / math.sqrt(hd), window=W, folded=True, gate=gate), 1, a.iters, a.warmup)
+    keys = sum(min(p + 1, W) if W else p + 1 for p in range(T))
+    flops = 2.0 * keys * H * hd * (K + 1)
+    return {"kernel": "flash_mix", "tokens": T, "H": H, "K": K, "hd": hd, "window": W, "us": round(us, 2), "TFLOPs": round(flops / us / 1e6, 1)}
+
+
+def bench_decay_attn(a) -> dict:
+    """Linear attention with decay, chunk by chunk, one sequence of --tokens."""
+    dev = "cuda:0"
+    H, hd, T = a.heads, a.head_dim, a.tokens
+    proj = torch.randn(T, 3 * H * hd, device=dev, dtype=torch.bfloat16)
+    q, k, v = (proj[:, i * H * hd: (i + 1) * H * hd] for i in range(3))
+    decay = torch.full((H,), 0.99, device=dev)
+    state = torch.zeros(1, H, hd, hd, device=dev)
+    slots = torch.zeros(1, dtype=torch.int32, device=dev)
+    start = torch.tensor([0, T], dtype=torch.int32, device=dev)
+    scratch = torch.empty(ops.decay_attn_chunked_scratch_floats(1, T, H, hd, hd), device=dev)
+    us = _time(lambda i: ops.decay_attn(q, k, v, decay, state, slots, start, H, hd, hd, silu=True, max_q_len=T, scratch=scratch), 1, a.iters, a.warmup)
+    flops = 2.0 * T * H * hd * (2 * hd + ops.DECAY_CHUNK)  # state update, state read, and the chunk's own scores and values
+    return {"kernel": "decay_attn (chunked, three kernels)", "tokens": T, "H": H, "hd": hd, "us": round(us, 2), "fp32_TFLOPs": round(flops / us / 1e6, 2)}
+
+
 def bench_rows(a) -> dict:
     dev = "cuda:0"
     d = a.k
@@ -415,7 +448,7 @@ def bench_probe_mma(a) -> dict:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kernel", choices=["gemv", "gemm", "linear", "attn_decode", "flash_prefill", "add_rmsnorm", "sample", "step_trace", "probe_stream", "probe_handshake", "probe_mma"])
+    ap.add_argument("kernel", choices=["gemv", "gemm", "linear", "attn_decode", "flash_prefill", "flash_mix", "decay_attn", "add_rmsnorm", "sample", "step_trace", "probe_stream", "probe_handshake", "probe_mma"])
     ap.add_argument("--rows", type=int, default=8)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -425,6 +458,7 @@ def main(argv=None) -> int:
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--window", type=int, default=1024, help="flash_mix: keys a query sees (0 = all)")
     ap.add_argument("--layers", type=int, default=4, help="step_trace: layers of the model")
     ap.add_argument("--ff", type=int, default=14336, help="step_trace: width of the feed-forward")
     ap.add_argument("--vocab", type=int, default=128256, help="step_trace, sample: vocabulary")
@@ -440,7 +474,7 @@ def main(argv=None) -> int:
     global USE_GRAPH
     USE_GRAPH = not a.no_graph
     fn = {"gemv": bench_gemv, "gemm": bench_gemm, "linear": bench_linear, "attn_decode": bench_attn_decode, "flash_prefill": bench_flash_prefill,
-          "add_rmsnorm": bench_rows, "sample": bench_sample, "step_trace": bench_step_trace, "probe_stream": bench_probe_stream,
+          "flash_mix": bench_flash_mix, "decay_attn": bench_decay_attn, "add_rmsnorm": bench_rows, "sample": bench_sample, "step_trace": bench_step_trace, "probe_stream": bench_probe_stream,
           "probe_handshake": bench_probe_handshake, "probe_mma": bench_probe_mma}[a.kernel]
     print(json.dumps(fn(a)))
     return 0
