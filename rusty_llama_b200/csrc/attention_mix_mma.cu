@@ -356,3 +356,286 @@ RL_API int rl_flash_mix(const void* q, long long q_row_stride, int q_head_stride
 #undef RL_MIX
   RL_REFUSE(9, "flash_mix: head size %d exceeds 256", hd);
 }
+
+// ---------------------------------------------------------------- decode steps: the rows of a block are HEADS
+// One query token per sequence.  A block takes one sequence and one part of its key range, with the folded queries of ALL
+// heads as the rows of its products (a warp per 16 heads): a key tile of kv head c is read once and meets part c of every
+// head's query, where a block per head would read every kv head's keys again for every head.  The values differ from row
+// to row (head h reads kv head h / (H / K)): for each kv head in turn the probabilities of the rows that do not read it are
+// set to zero before the product, and all rows add into one accumulator.  Each block leaves its maximum (base-2 exponent),
+// sum and unnormalised result per head; `flash_mix_merge_kernel` adds the parts of a key range up and applies gate and factor.
+template <int HD>
+__global__ void flash_mix_decode_kernel(const bf16* __restrict__ qf, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+                                        const int* __restrict__ block_table, int table_width, const int* __restrict__ seq_pos0,
+                                        const float* __restrict__ sink, float* __restrict__ part_o, float* __restrict__ part_ml, int H,
+                                        int K, int kdim, int vdim, int window, float scale_log2, int n_splits) {
+  constexpr int STRIDE = HD + 8;
+  constexpr int KSTEPS = HD / 16;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* ring = reinterpret_cast<bf16*>(smem_raw);  // NBUF x [BN][STRIDE]
+  bf16* q_s = ring + NBUF * BN * STRIDE;           // K x [rows][STRIDE], rows = 16 * warps
+  const int nthreads = blockDim.x, rows = nthreads >> 1;
+  const int split = blockIdx.x, s = blockIdx.y;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int rep = H / K;
+  const int pos = seq_pos0[s];  // the token's own position; its key and value are in the cache already
+  const int first = (window != 0 && pos + 1 > window) ? pos + 1 - window : 0;
+  const int tile_first = first / BN, n_tiles = pos / BN - tile_first + 1;
+  const int per = (n_tiles + n_splits - 1) / n_splits;
+  const int tile_lo = tile_first + split * per, tile_hi = min(tile_first + n_tiles, tile_lo + per) - 1;
+  const int r_lo = warp * 16 + g, r_hi = r_lo + 8;  // this thread's two rows (heads)
+
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.f, 0.f};
+  float o_acc[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
+  if (sink != nullptr && split == 0) {
+    if (r_lo < H) {
+      m_run[0] = sink[r_lo] * 1.4426950408889634f;
+      l_run[0] = (t4 == 0) ? 1.f : 0.f;
+    }
+    if (r_hi < H) {
+      m_run[1] = sink[r_hi] * 1.4426950408889634f;
+      l_run[1] = (t4 == 0) ? 1.f : 0.f;
+    }
+  }
+  if (tile_lo <= tile_hi) {
+    {
+      uint4 z = make_uint4(0, 0, 0, 0);
+      uint4* p = reinterpret_cast<uint4*>(smem_raw);
+      const int n16 = ((NBUF * BN + K * rows) * STRIDE * (int)sizeof(bf16)) / 16;
+      for (int i = tid; i < n16; i += nthreads) p[i] = z;
+    }
+    __syncthreads();
+    const int chunks = kdim >> 3;
+    const bf16* qrow = qf + (size_t)s * H * K * kdim;  // [H][K][kdim]
+    for (int c = tid; c < H * K * chunks; c += nthreads) {
+      const int cc = c % chunks, hp = c / chunks, part = hp % K, h = hp / K;
+      cp_async_16(q_s + ((size_t)part * rows + h) * STRIDE + cc * 8, qrow + (size_t)hp * kdim + cc * 8);
+    }
+    const int* table = block_table + (size_t)s * table_width;
+    const int per_tile = 2 * K;
+    const int n_loads = (tile_hi - tile_lo + 1) * per_tile;
+    auto issue = [&](int n) {
+      const int tile = tile_lo + n / per_tile, part = n % per_tile;
+      bf16* dst = ring + (size_t)(n % NBUF) * BN * STRIDE;
+      const size_t page = (size_t)table[tile];
+      const bool is_k = part < K;
+      const int kv = is_k ? part : part - K, width = is_k ? kdim : vdim;
+      const bf16* src = (is_k ? k_pages : v_pages) + ((page * K + kv) * BN) * width;
+      const int ch = width >> 3;
+      for (int c = tid; c < BN * ch; c += nthreads) {
+        const int r = c / ch, cc = c - r * ch;
+        cp_async_16(dst + (size_t)r * STRIDE + cc * 8, src + (size_t)r * width + cc * 8);
+      }
+    };
+    issue(0);
+    cp_async_commit();
+    if (n_loads > 1) issue(1);
+    cp_async_commit();
+    float s_acc[BN / 8][4];
+    // kv heads that this warp's sixteen rows read
+    const int c_first = (warp * 16) / rep, c_last = min(H - 1, warp * 16 + 15) / rep;
+    const int kv_lo = r_lo / rep, kv_hi = r_hi / rep;
+    for (int n = 0; n < n_loads; ++n) {
+      if (n + 2 < n_loads) issue(n + 2);
+      cp_async_commit();
+      cp_async_wait<2>();
+      __syncthreads();
+      const int tile = tile_lo + n / per_tile, part = n % per_tile;
+      const bf16* buf = ring + (size_t)(n % NBUF) * BN * STRIDE;
+      if (part < K) {
+        if (part == 0) {
+#pragma unroll
+          for (int i = 0; i < BN / 8; ++i) s_acc[i][0] = s_acc[i][1] = s_acc[i][2] = s_acc[i][3] = 0.f;
+        }
+        const bf16* qp = q_s + (size_t)part * rows * STRIDE;
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) {
+          uint32_t a[4];
+          ldmatrix_x4(a, qp + (size_t)(warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * STRIDE + kk * 16 + 8 * (lane >> 4));
+#pragma unroll
+          for (int np = 0; np < BN / 16; ++np) {
+            uint32_t b[4];
+            ldmatrix_x4(b, buf + (size_t)(np * 16 + (lane & 7) + 8 * (lane >> 4)) * STRIDE + kk * 16 + 8 * ((lane >> 3) & 1));
+            mma_bf16(s_acc[2 * np], a, b[0], b[1]);
+            mma_bf16(s_acc[2 * np + 1], a, b[2], b[3]);
+          }
+        }
+      } else {
+        const int c = part - K;
+        if (c == 0) {
+          // ---- the tile's scores are complete: mask, scale and the online softmax, once per tile
+          const int key0 = tile * BN;
+          float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+          for (int nn = 0; nn < BN / 8; ++nn) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int key = key0 + nn * 8 + 2 * t4 + (e & 1);
+              float v = s_acc[nn][e] * scale_log2;
+              if (key > pos || key < first) v = -INFINITY;
+              s_acc[nn][e] = v;
+              tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
+            }
+          }
+          float alpha[2], m_use[2];
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            float mx = tile_max[r];
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m_run[r], mx);
+            m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;
+            alpha[r] = exp2f(m_run[r] - m_use[r]);
+            m_run[r] = m_new;
+            l_run[r] *= alpha[r];
+          }
+#pragma unroll
+          for (int nn = 0; nn < BN / 8; ++nn) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float p = exp2f(s_acc[nn][e] - m_use[e >> 1]);
+              s_acc[nn][e] = p;
+              l_run[e >> 1] += p;
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < HD / 8; ++i) {
+            o_acc[i][0] *= alpha[0];
+            o_acc[i][1] *= alpha[0];
+            o_acc[i][2] *= alpha[1];
+            o_acc[i][3] *= alpha[1];
+          }
+        }
+        // ---- O += (P of the rows that read kv head c) V_c
+        if (c >= c_first && c <= c_last) {
+          const bool lo = kv_lo == c, hi = kv_hi == c;
+#pragma unroll
+          for (int kk = 0; kk < BN / 16; ++kk) {
+            uint32_t a[4];
+            a[0] = lo ? pack_bf16(s_acc[2 * kk][0], s_acc[2 * kk][1]) : 0u;
+            a[1] = hi ? pack_bf16(s_acc[2 * kk][2], s_acc[2 * kk][3]) : 0u;
+            a[2] = lo ? pack_bf16(s_acc[2 * kk + 1][0], s_acc[2 * kk + 1][1]) : 0u;
+            a[3] = hi ? pack_bf16(s_acc[2 * kk + 1][2], s_acc[2 * kk + 1][3]) : 0u;
+#pragma unroll
+            for (int dp = 0; dp < HD / 16; ++dp) {
+              uint32_t b[4];
+              ldmatrix_x4_trans(b, buf + (size_t)(kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * STRIDE + dp * 16 + 8 * (lane >> 4));
+              mma_bf16(o_acc[2 * dp], a, b[0], b[1]);
+              mma_bf16(o_acc[2 * dp + 1], a, b[2], b[3]);
+            }
+          }
+        }
+      }
+      __syncthreads();
+    }
+  }
+  // ---- this part's maximum, sum and unnormalised result per head
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    float l = l_run[r];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    const int h = r ? r_hi : r_lo;
+    if (h < H) {
+      const size_t slot = ((size_t)s * H + h) * n_splits + split;
+      if (t4 == 0) {
+        part_ml[slot * 2] = m_run[r];
+        part_ml[slot * 2 + 1] = l;
+      }
+      float* po = part_o + slot * vdim;
+#pragma unroll
+      for (int nn = 0; nn < HD / 8; ++nn) {
+        const int d = nn * 8 + 2 * t4;
+        if (d < vdim) {
+          po[d] = o_acc[nn][2 * r];
+          po[d + 1] = o_acc[nn][2 * r + 1];
+        }
+      }
+    }
+  }
+}
+
+// grid (H, S): out[s][h] = sum over the parts of the key range, normalised, times sigmoid(gate) and the factor.
+__global__ void flash_mix_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const bf16* __restrict__ gate,
+                                       int gate_stride, float out_scale, bf16* __restrict__ out, int out_stride, int H, int vdim,
+                                       int n_splits) {
+  const int h = blockIdx.x, s = blockIdx.y;
+  const size_t base = ((size_t)s * H + h) * n_splits;
+  float M = -INFINITY;
+  for (int i = 0; i < n_splits; ++i) M = fmaxf(M, part_ml[(base + i) * 2]);
+  float denom = 0.f;
+  for (int i = 0; i < n_splits; ++i) {
+    const float m = part_ml[(base + i) * 2];
+    denom += ((m == -INFINITY) ? 0.f : exp2f(m - M)) * part_ml[(base + i) * 2 + 1];
+  }
+  const float inv = denom > 0.f ? out_scale / denom : 0.f;
+  for (int d = threadIdx.x; d < vdim; d += blockDim.x) {
+    float acc = 0.f;
+    for (int i = 0; i < n_splits; ++i) {
+      const float m = part_ml[(base + i) * 2];
+      if (m != -INFINITY) acc += exp2f(m - M) * part_o[(base + i) * vdim + d];
+    }
+    acc *= inv;
+    if (gate) acc *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)s * gate_stride + (size_t)h * vdim + d])));
+    out[(size_t)s * out_stride + (size_t)h * vdim + d] = __float2bfloat16_rn(acc);
+  }
+}
+
+template <int HD>
+static int launch_mix_decode(const bf16* qf, const bf16* k_pages, const bf16* v_pages, const int* block_table, int table_width,
+                             const int* seq_pos0, const float* sink, const bf16* gate, int gate_stride, float out_scale, float* part_o,
+                             float* part_ml, bf16* out, int out_stride, int n_seqs, int H, int K, int kdim, int vdim, int window, float scale,
+                             int n_splits, cudaStream_t stream) {
+  const int warps = (H + 15) / 16;
+  const size_t smem = (size_t)(NBUF * BN + K * warps * 16) * (HD + 8) * sizeof(bf16);
+  auto kern = flash_mix_decode_kernel<HD>;
+  if (smem > 227 * 1024) RL_REFUSE(8, "flash_mix_decode: %zu bytes of shared memory exceed the SM's", smem);
+  if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    RL_REFUSE(8, "flash_mix_decode: cannot get %zu bytes of shared memory", smem);
+  dim3 grid(n_splits, n_seqs);
+  kern<<<grid, warps * 32, smem, stream>>>(qf, k_pages, v_pages, block_table, table_width, seq_pos0, sink, part_o, part_ml, H, K, kdim, vdim,
+                                           window, scale * 1.4426950408889634f, n_splits);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    snprintf(rl_error_buf, sizeof(rl_error_buf), "%s", cudaGetErrorString(e));
+    return (int)e;
+  }
+  dim3 grid2(H, n_seqs);
+  flash_mix_merge_kernel<<<grid2, 64, 0, stream>>>(part_o, part_ml, gate, gate_stride, out_scale, out, out_stride, H, vdim, n_splits);
+  RL_LAUNCH_RESULT();
+}
+
+RL_API int rl_flash_mix_decode_smem(int H, int K, int hd_max) {
+  const int HD = hd_max <= 32 ? 32 : (hd_max <= 64 ? 64 : (hd_max <= 128 ? 128 : 256));
+  return (NBUF * BN + K * ((H + 15) / 16) * 16) * (HD + 8) * (int)sizeof(bf16);
+}
+
+// qf: folded queries [S][H][K][kdim] (`rl_fold_queries`; with the identity as mixing matrix for an attention without mixing).
+// seq_pos0[s]: the position of sequence s's token.  part_o: S * H * n_splits * vdim floats, part_ml: S * H * n_splits * 2.
+RL_API int rl_flash_mix_decode(const void* qf, const void* k_pages, const void* v_pages, const int* block_table, int table_width,
+                               const int* seq_pos0, const float* sink, const void* gate, int gate_stride, float out_scale, float* part_o,
+                               float* part_ml, void* out, int out_stride, int n_seqs, int H, int K, int kdim, int vdim, int page_size,
+                               int window, float scale, int n_splits, cudaStream_t stream) {
+  if (n_seqs <= 0 || H <= 0 || K <= 0 || kdim <= 0 || vdim <= 0 || n_splits <= 0 || !part_o || !part_ml)
+    RL_REFUSE(1, "flash_mix_decode: S=%d H=%d K=%d kdim=%d vdim=%d splits=%d", n_seqs, H, K, kdim, vdim, n_splits);
+  if (H % K || H > 256) RL_REFUSE(2, "flash_mix_decode: %d heads on %d kv heads (at most 256 heads)", H, K);
+  if (page_size != BN) RL_REFUSE(3, "flash_mix_decode: page size %d, this kernel is built for %d", page_size, BN);
+  if (kdim % 8 || vdim % 8) RL_REFUSE(4, "flash_mix_decode: key and value sizes %d / %d must be multiples of 8", kdim, vdim);
+  if (((uintptr_t)qf | (uintptr_t)k_pages | (uintptr_t)v_pages) % 16) RL_REFUSE(5, "flash_mix_decode: addresses break the alignment of 16-byte copies");
+  if (window < 0 || n_seqs > 65535) RL_REFUSE(6, "flash_mix_decode: window %d, %d sequences", window, n_seqs);
+  const int hd = kdim > vdim ? kdim : vdim;
+#define RL_MIXD(HDV)                                                                                                                    \
+  return launch_mix_decode<HDV>((const bf16*)qf, (const bf16*)k_pages, (const bf16*)v_pages, block_table, table_width, seq_pos0, sink,    \
+                                (const bf16*)gate, gate_stride, out_scale, part_o, part_ml, (bf16*)out, out_stride, n_seqs, H, K, kdim,    \
+                                vdim, window, scale, n_splits, stream)
+  if (hd <= 32) RL_MIXD(32);
+  if (hd <= 64) RL_MIXD(64);
+  if (hd <= 128) RL_MIXD(128);
+  if (hd <= 256) RL_MIXD(256);
+#undef RL_MIXD
+  RL_REFUSE(9, "flash_mix_decode: head size %d exceeds 256", hd);
+}

@@ -1533,3 +1533,59 @@ def flash_mix(
     )
     _check(lib, rc, "flash_mix")
     return out
+
+
+def flash_mix_decode_takes(num_heads: int, num_kv_heads: int, kdim: int, vdim: int) -> bool:
+    """Whether `flash_mix_decode` (and `fold_queries` before it) is built for these sizes."""
+    if kdim % 8 or vdim % 8 or max(kdim, vdim) > 256 or num_heads > 256:
+        return False
+    hd = max(kdim, vdim)
+    hd = 32 if hd <= 32 else 64 if hd <= 64 else 128 if hd <= 128 else 256
+    rows = (num_heads + 15) // 16 * 16
+    return ((3 * 64 + num_kv_heads * rows) * (hd + 8) * 2 <= FLASH_MIX_SMEM_LIMIT
+            and (num_heads * kdim + num_heads * num_heads) * 4 <= 48 * 1024)
+
+
+def flash_mix_decode_scratch_floats(n_seqs: int, num_heads: int, vdim: int, n_splits: int) -> int:
+    return n_seqs * num_heads * n_splits * (vdim + 2)
+
+
+def flash_mix_decode(
+    qf: torch.Tensor, k_pages, v_pages, block_table, seq_pos0, num_heads: int, num_kv_heads: int, kdim: int, vdim: int, scale: float,
+    n_splits: int, scratch: torch.Tensor, window: int = 0, sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+    out_scale: float = 1.0, out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """One query token per sequence, at position seq_pos0[s], over its sequence's cached keys (its own among them), the key range
+    cut into `n_splits` parts; a block's rows are the heads.  qf: folded queries [S, H K kdim] (`fold_queries`, with the identity
+    matrix for an attention without mixing).  scratch: float32, `flash_mix_decode_scratch_floats(...)`."""
+    _cuda(qf, "flash_mix_decode qf", torch.bfloat16)
+    S = qf.shape[0]
+    _need(qf.dim() == 2 and qf.shape[1] == num_heads * num_kv_heads * kdim, "flash_mix_decode: qf must be [S, H K kdim]")
+    _need(flash_mix_decode_takes(num_heads, num_kv_heads, kdim, vdim), f"flash_mix_decode: sizes {num_heads} / {num_kv_heads} / {kdim} / {vdim} are not built")
+    _check_kv_pages(k_pages, v_pages, torch.bfloat16, num_kv_heads, kdim, vdim, "flash_mix_decode")
+    _cuda(block_table, "flash_mix_decode block_table", torch.int32)
+    _cuda(seq_pos0, "flash_mix_decode seq_pos0", torch.int32)
+    _need(seq_pos0.numel() == S and block_table.dim() == 2 and block_table.shape[0] >= S, "flash_mix_decode: metadata sizes")
+    _need(1 <= n_splits <= 256, f"flash_mix_decode: {n_splits} splits")
+    _check_sink(sink, num_heads, "flash_mix_decode")
+    _cuda(scratch, "flash_mix_decode scratch", torch.float32)
+    _need(scratch.numel() >= flash_mix_decode_scratch_floats(S, num_heads, vdim, n_splits), "flash_mix_decode: scratch too small")
+    gs = 0
+    if gate is not None:
+        _cuda(gate, "flash_mix_decode gate", torch.bfloat16, contiguous=False)
+        gs = _rows(gate, "flash_mix_decode gate")
+        _need(gate.shape[0] == S and gate.shape[1] >= num_heads * vdim, "flash_mix_decode: gate rows too short")
+    if out is None:
+        out = torch.empty((S, num_heads * vdim), dtype=torch.bfloat16, device=qf.device)
+    _cuda(out, "flash_mix_decode out", torch.bfloat16, contiguous=False)
+    _need(tuple(out.shape) == (S, num_heads * vdim) and _rows(out, "flash_mix_decode out") >= num_heads * vdim, "flash_mix_decode: out must be [S, H vdim]")
+    n_o = S * num_heads * n_splits * vdim
+    lib = build.load("attention_mix_mma")
+    rc = lib.rl_flash_mix_decode(
+        _p(qf), _p(k_pages), _p(v_pages), _p(block_table), c_int(block_table.shape[1]), _p(seq_pos0), _p(sink), _p(gate), c_int(gs),
+        c_float(out_scale), c_void_p(scratch.data_ptr()), c_void_p(scratch.data_ptr() + 4 * n_o), _p(out), c_int(out.stride(0)), c_int(S),
+        c_int(num_heads), c_int(num_kv_heads), c_int(kdim), c_int(vdim), c_int(PAGE_SIZE), c_int(window), c_float(scale), c_int(n_splits),
+        _stream(),
+    )
+    _check(lib, rc, "flash_mix_decode", kernels=2)
+    return out

@@ -104,7 +104,14 @@ def kernel_table(z: dict, T: int, batch: int, ctx: int, peaks: dict) -> Dict[str
             us_fold = mb._time(lambda i: ops.fold_queries(q, mix, H, G, hd), 1, **it)
             note(f"{tag}_fold_queries", us_fold, rows * H * hd * 2 * (1 + G), 2.0 * rows * H * H * hd)
             qf = ops.fold_queries(q, mix, H, G, hd)
-            us = mb._time(lambda i: ops.flash_mix(qf, kp, vp, table, start, p0, max_q, H, G, hd, hd, scale, window=W, folded=True, gate=gate), 1, **it)
+            if rows > batch or not ops.flash_mix_decode_takes(H, G, hd, hd):
+                us = mb._time(lambda i: ops.flash_mix(qf, kp, vp, table, start, p0, max_q, H, G, hd, hd, scale, window=W, folded=True, gate=gate), 1, **it)
+            else:  # a decode step: the rows of a block are the heads (as `Attention` plans it)
+                from .device import sm_count
+                pages = (min(W, pos0 + 1) + 63) // 64 + 1
+                n_splits = max(1, min(2 * sm_count() // n_seqs, pages // 2, 64))
+                sc = torch.empty(ops.flash_mix_decode_scratch_floats(n_seqs, H, hd, n_splits), device=dev)
+                us = mb._time(lambda i: ops.flash_mix_decode(qf, kp, vp, table, p0, H, G, hd, hd, scale, n_splits, sc, window=W, gate=gate), 1, **it)
             # its products: the scores against the keys of all kv heads, and the values
             note(f"{tag}_attention_mixed_window_gate", us, cache_bytes(min(W, pos0 + rows // n_seqs)) + rows * H * hd * (2 * G + 4), 2.0 * keys_win * H * hd * (G + 1),
                  like=like_prefill if rows > batch else like_decode)

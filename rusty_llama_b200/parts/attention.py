@@ -118,6 +118,7 @@ class Attention(Mixer):
         self.w_qkv = None
         self.w_o = None
         self.b_in = self.b_o = self.sink = self.mix = None
+        self.fold_matrix = None  # what `fold_queries` mixes by in a decode step: the mixing matrix, or the identity
 
     def cache_need(self):
         return KVNeed(self.K, self.hd, self.window, value_dim=self.vd if self.vd != self.hd else None)
@@ -179,7 +180,23 @@ class Attention(Mixer):
         parts = self.K if self.has_mix else 1
         if (self.rt.dtype == torch.bfloat16 and ops.flash_mix_takes(self.hd, self.vd, parts) and proj.stride(0) % 8 == 0
                 and (out is None or (out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0)) and (self.qd + self.kvd + self.vvd) % 2 == 0):
-            # the tensor-core kernel, for prompts and single tokens alike; mixed scores come from folded queries
+            if step.decode_only and ops.flash_mix_decode_takes(self.H, self.K, self.hd, self.vd):
+                # single tokens: all heads of a sequence are the rows of one block, which reads a key tile once for all of them;
+                # the key range is cut into parts of at least two pages so that the blocks fill the GPU once
+                if self.fold_matrix is None:
+                    self.fold_matrix = self.mix if self.has_mix else torch.eye(self.H, dtype=torch.float32, device=xn.device)
+                qf = ops.fold_queries(proj, self.fold_matrix, self.H, self.K, self.hd)
+                keys = min(self.window, step.plan_kv_len) if self.window else step.plan_kv_len
+                pages = (keys + ops.PAGE_SIZE - 1) // ops.PAGE_SIZE + 1
+                n_splits = max(1, min(2 * sm_count(xn.device) // step.n_seqs, pages // 2, 64))
+                scratch = self.rt.workspace.get("flash_mix_decode", ops.flash_mix_decode_scratch_floats(step.n_seqs, self.H, self.vd, n_splits), torch.float32)
+                a = ops.flash_mix_decode(
+                    qf, cache.k_pages, cache.v_pages, cache.block_table, step.seq_pos0, self.H, self.K, self.hd, self.vd, self.scale,
+                    n_splits, scratch, window=self.window, sink=self.sink, gate=gate, out_scale=self.out_scale, out=out,
+                )
+                return a, self.w_o
+            # the tensor-core kernel for prompts (and single tokens of sizes the decode kernel does not take); mixed scores come
+            # from folded queries
             q = ops.fold_queries(proj, self.mix, self.H, self.K, self.hd) if self.has_mix else proj
             a = ops.flash_mix(
                 q, cache.k_pages, cache.v_pages, cache.block_table, step.seq_start, step.seq_pos0, step.max_q_len, self.H, self.K,

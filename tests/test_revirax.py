@@ -544,8 +544,9 @@ def test_row_kernels(dtype):
     assert np.abs(out.to(torch.float64).cpu().numpy() - ref).max() <= _tol(dtype, 1e-5, 2e-2) * np.abs(ref).max()
 
 
+@pytest.mark.parametrize("window", [0, 70])
 @pytest.mark.parametrize("hd, H, G", [(64, 8, 2), (128, 4, 4), (48, 6, 3), (24, 2, 1)])
-def test_sink_on_the_tensor_core_attention_kernels(hd, H, G):
+def test_sink_on_the_tensor_core_attention_kernels(hd, H, G, window):
     """The bfloat16 kernels of a plain attention with a sink: a prompt that goes on from position 70 with 90 tokens (both prompt
     kernels where the head size allows), then single tokens at positions around page borders with the key range in one part
     and in several (both decode kernels).  Sinks of the size of the scores, one very large, one very small."""
@@ -560,13 +561,13 @@ def test_sink_on_the_tensor_core_attention_kernels(hd, H, G):
     kp, vp, table = _paged_kv(k, v, dt, 7, [5, 0, 3, 6, 2])
     sink_t = _dev(sink, torch.float32)
     q_all = _rounded(rng.standard_normal((L, H, hd)), dt)
-    ref = pr.softmax_attention(q_all, k, v, scale, 0, sink, None)
+    ref = pr.softmax_attention(q_all, k, v, scale, window, sink, None)
     # prompt: rows 70 .. 159
     q = _dev(q_all[70:160].reshape(90, H * hd), dt)
     start, pos0 = _i32([0, 90]), _i32([70])
-    outs = {"flash_prefill": ops.flash_prefill(q, kp, vp, table, start, pos0, 90, H, G, hd, scale=scale, sink=sink_t)}
+    outs = {"flash_prefill": ops.flash_prefill(q, kp, vp, table, start, pos0, 90, H, G, hd, scale=scale, sink=sink_t, window=window)}
     if hd in ops.FLASH_TC_HEAD_DIMS:
-        outs["flash_prefill_tc"] = ops.flash_prefill_tc(q, kp, vp, table, start, pos0, 90, H, G, hd, scale=scale, sink=sink_t)
+        outs["flash_prefill_tc"] = ops.flash_prefill_tc(q, kp, vp, table, start, pos0, 90, H, G, hd, scale=scale, sink=sink_t, window=window)
     for name, out in outs.items():
         err = np.abs(out.to(torch.float64).cpu().numpy() - ref[70:160]).max()
         assert err <= 2e-2 * max(1.0, np.abs(ref).max()), (name, err)
@@ -576,7 +577,7 @@ def test_sink_on_the_tensor_core_attention_kernels(hd, H, G):
         for impl in ("warp",) + (("tma",) if hd in ops.ATTN_DECODE_TMA_HEAD_DIMS else ()):
             for n_splits in (1, 3):
                 scratch = torch.empty(ops.attn_decode_scratch_floats(1, H, hd, n_splits), dtype=torch.float32, device="cuda")
-                out = ops.attn_decode(qd, kp, vp, table, _i32([p + 1]), H, G, hd, n_splits, scratch, scale=scale, impl=impl, sink=sink_t)
+                out = ops.attn_decode(qd, kp, vp, table, _i32([p + 1]), H, G, hd, n_splits, scratch, scale=scale, impl=impl, sink=sink_t, window=window)
                 err = np.abs(out.to(torch.float64).cpu().numpy()[0] - ref[p]).max()
                 assert err <= 2e-2 * max(1.0, np.abs(ref).max()), (impl, n_splits, p, err)
     ops.tc_status_check()
@@ -641,6 +642,16 @@ def test_tensor_core_attention_with_options(H, G, kd, vd, window, talk, use_sink
                             sink=None if sink is None else _dev(sink, torch.float32), folded=talk)
         err = np.abs(out.to(torch.float64).cpu().numpy()[0] - full[p]).max()
         assert err <= 2.5e-2 * max(1.0, np.abs(full).max()), (p, err)
+        # the decode kernel whose rows are the heads, with the key range in one part, in three and in more parts than pages
+        fold = _dev(mix if talk else np.eye(H), torch.float32)
+        g1 = _rounded(rng.standard_normal((1, H * vd)), dt)
+        for n_splits in (1, 3, 7):
+            scratch = torch.full((ops.flash_mix_decode_scratch_floats(1, H, vd, n_splits),), float("nan"), device="cuda")
+            out = ops.flash_mix_decode(ops.fold_queries(q1, fold, H, G, kd), kp, vp, torch.from_numpy(table[:1]).cuda(), _i32([p]), H, G, kd, vd, scale,
+                                       n_splits, scratch, window=window, sink=None if sink is None else _dev(sink, torch.float32), gate=_dev(g1, dt), out_scale=1.4)
+            want = full[p] * pr.sigmoid(g1[0]) * 1.4
+            err = np.abs(out.to(torch.float64).cpu().numpy()[0] - want).max()
+            assert err <= 2.5e-2 * max(1.0, np.abs(full).max()), (p, n_splits, err)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
