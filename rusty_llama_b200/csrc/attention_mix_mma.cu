@@ -64,12 +64,25 @@ fold_queries_kernel(const bf16* __restrict__ q, int q_stride, const float* __res
   float* m_s = fq_s + H * kdim;
   const int t = blockIdx.x, rep = H / K;
   const bf16* row = q + (size_t)t * q_stride;
-  for (int i = threadIdx.x; i < H * kdim; i += blockDim.x) q_s[i] = __bfloat162float(row[i]);
-  for (int i = threadIdx.x; i < H * H; i += blockDim.x) m_s[i] = mix[i];
+  if (((H * kdim) & 7) == 0 && (((uintptr_t)row) & 15) == 0) {  // sixteen bytes a load, all of a thread's loads in flight at once
+#pragma unroll 4
+    for (int i = threadIdx.x * 8; i < H * kdim; i += blockDim.x * 8) {
+      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(row + i));
+      float f[8];
+      bf16x8_to_f32(raw, f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) q_s[i + e] = f[e];
+    }
+  } else {
+    for (int i = threadIdx.x; i < H * kdim; i += blockDim.x) q_s[i] = __bfloat162float(row[i]);
+  }
+#pragma unroll 4
+  for (int i = threadIdx.x; i < H * H; i += blockDim.x) m_s[i] = __ldg(mix + i);
   __syncthreads();
   bf16* o = out + (size_t)t * H * K * kdim;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  for (int hc = warp; hc < H * K; hc += nw) {
+  // (a step of few tokens spreads a token's parts over gridDim.y blocks)
+  for (int hc = blockIdx.y * nw + warp; hc < H * K; hc += nw * gridDim.y) {
     const int h = hc / K, c = hc - h * K;
     const float* m = m_s + h * H + c * rep;
     const float* qg = q_s + (size_t)c * rep * kdim;
@@ -86,7 +99,8 @@ RL_API int rl_fold_queries(const void* q, int q_stride, const float* mix, void* 
   if (n_tokens <= 0 || H <= 0 || K <= 0 || kdim <= 0 || H % K || !q || !mix || !out) RL_REFUSE(1, "fold_queries: T=%d H=%d K=%d kdim=%d", n_tokens, H, K, kdim);
   const size_t smem = ((size_t)H * kdim + (size_t)H * H) * sizeof(float);
   if (smem > 48 * 1024) RL_REFUSE(2, "fold_queries: %d heads of %d numbers do not fit shared memory", H, kdim);
-  fold_queries_kernel<<<n_tokens, 256, smem, stream>>>((const bf16*)q, q_stride, mix, (bf16*)out, H, K, kdim);
+  dim3 grid(n_tokens, n_tokens >= 64 ? 1 : 8);
+  fold_queries_kernel<<<grid, 256, smem, stream>>>((const bf16*)q, q_stride, mix, (bf16*)out, H, K, kdim);
   RL_LAUNCH_RESULT();
 }
 

@@ -381,10 +381,12 @@ __global__ void rms_gate_kernel(const float* __restrict__ x, int x_stride, const
   const int t = blockIdx.x;
   const float* xr = x + (size_t)t * x_stride;
   float ss = 0.f;
+#pragma unroll 8
   for (int i = threadIdx.x; i < n; i += blockDim.x) ss += xr[i] * xr[i];
   const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)n + eps);
   const T* g = gate ? gate + (size_t)t * gate_stride : nullptr;
   T* o = out + (size_t)t * out_stride;
+#pragma unroll 4
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     float y = xr[i] * inv * to_f32(w[i]);
     if (g) y *= logistic(to_f32(g[i]));
