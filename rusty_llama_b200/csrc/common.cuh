@@ -117,6 +117,18 @@ __device__ __forceinline__ float gated_act_fast(float g, float u, float alpha, f
   return __fdividef(g, 1.0f + __expf(-g)) * u;
 }
 
+// A product that is not a gate/up product may send its 32-bit sums through an activation of one argument before they are
+// stored.  The launchers that take (act_alpha, act_limit) for a gate/up product take its code in act_limit otherwise:
+// RL_UNARY_RELU2 is relu(x)^2; anything else leaves the sums as they are.
+#define RL_UNARY_RELU2 (-2.0f)
+__device__ __forceinline__ float unary_post(float v, float code) {
+  if (code == RL_UNARY_RELU2) {
+    v = fmaxf(v, 0.f);
+    return v * v;
+  }
+  return v;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -368,6 +368,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           tmem_ld_32x32b_x32(lane_base + (uint32_t)(c * 32), r0);
           tmem_ld_32x32b_x32(lane_base + (uint32_t)(c * 32 + 32), r1);
           tmem_ld_wait();
+          if (!SWIGLU && act_limit == RL_UNARY_RELU2) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              r0[i] = __float_as_uint(unary_post(__uint_as_float(r0[i]), act_limit));
+              r1[i] = __float_as_uint(unary_post(__uint_as_float(r1[i]), act_limit));
+            }
+          }
           const int col = n0 + c * 32;
           bf16* tile_out = reinterpret_cast<bf16*>(out_k) + (size_t)(m0 + quarter * 32) * ldo + (SWIGLU ? (col >> 1) : col);
           if (SWIGLU)
@@ -381,6 +388,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         uint32_t r[32];
         tmem_ld_32x32b_x32(lane_base + (uint32_t)(c * 32), r);
         tmem_ld_wait();
+        if (!SWIGLU && act_limit == RL_UNARY_RELU2) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(unary_post(__uint_as_float(r[i]), act_limit));
+        }
         const int col = n0 + c * 32;
         const int n_valid = min(N - col, bn - c * 32);  // columns of this piece that belong to the tile and the matrix
         if (sizeof(TO) == 4 && !SWIGLU && vec_store && whole_rows && n_valid >= 32) {
@@ -436,6 +447,7 @@ RL_API int rl_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* out,
   if (out_dtype != RL_BF16 && out_dtype != RL_F32) RL_REFUSE(6, "gemm_tc: unknown output dtype %d", out_dtype);
   if (status == nullptr) RL_REFUSE(7, "gemm_tc: no status word");
   if (k_splits < 1) RL_REFUSE(12, "gemm_tc: %d k slices", k_splits);
+  if (k_splits > 1 && !swiglu && act_limit == RL_UNARY_RELU2) RL_REFUSE(13, "gemm_tc: partial sums over k slices cannot go through an activation");
   if (k_splits > 1 && (swiglu || out_dtype != RL_F32)) RL_REFUSE(13, "gemm_tc: partial sums over k slices are float32 and cannot go through the activation");
   if (tile_n != 0 && (tile_n < 16 || tile_n > BN || tile_n % 16)) RL_REFUSE(14, "gemm_tc: a tile width of %d (a multiple of 16 up to %d)", tile_n, BN);
   {

@@ -287,7 +287,7 @@ gemv_stream_kernel(const bf16* __restrict__ x, int ldx, const __grid_constant__ 
             fold.xw[(size_t)m * fold.xw_ld + n] = __float2bfloat16_rn(v * wn);
             ss += v * v;
           } else {
-            store_out<TO>(out_slice + (size_t)m * ldo + n, sum);
+            store_out<TO>(out_slice + (size_t)m * ldo + n, unary_post(sum, fold.act_limit));
           }
         }
       }
@@ -458,6 +458,8 @@ static int launch_gemv_stream(const void* x, int ldx, const void* w, int ldw, vo
   // (a caller that did not ask for slices has room for one result only)
   if (slices > 1 && (swiglu || out_dtype != RL_F32 || k_slices == 1))
     RL_REFUSE(8, "gemv_stream: k = %d comes in %d slices of at most %d, whose partial sums are float32, cannot go through the activation and have to be asked for (k_slices > 1)", K, slices, MAX_SLICE);
+  if (!swiglu && fold.act_limit == RL_UNARY_RELU2 && (slices > 1 || fold.resid != nullptr))
+    RL_REFUSE(8, "gemv_stream: only whole sums that are stored as they are can go through an activation (k = %d comes in %d slices)", K, slices);
   if (slices_used) *slices_used = slices;
   const int units = (N + UNIT_ROWS - 1) / UNIT_ROWS;
   const long long items_ll = (long long)units * slices;

@@ -48,30 +48,42 @@ def use_library_gemm(on: bool) -> None:
     _library_gemm = bool(on)
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """x[M, K] (dense rows), w[N, K] -> [M, N] in `out_dtype` (default: x's dtype)."""
+_UNARY = {"relu2": ops.ACT_RELU2}
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, act: Optional[str] = None) -> torch.Tensor:
+    """x[M, K] (dense rows), w[N, K] -> [M, N] in `out_dtype` (default: x's dtype).
+
+    act: None, or "relu2": the result is relu(x . w^T)^2.  The streaming and the tcgen05 kernel apply it to their 32-bit sums
+    before anything is rounded or stored; behind the other kernels it is a pass of its own."""
+    if act is not None and act not in _UNARY:
+        raise KernelError(f"linear: activation '{act}' is not built (known: {', '.join(_UNARY)})")
     if out_dtype is None:
         out_dtype = x.dtype
+
+    def after(y):
+        return y if act is None else ops.unary_act(y, _UNARY[act])
+
     if x.dtype == torch.float32:
         if w.dtype != torch.float32 or out_dtype != torch.float32:
             raise KernelError(f"linear: a float32 input needs float32 weights and output, got {w.dtype}, {out_dtype}")
-        return ops.gemm_f32(x, w)
+        return after(ops.gemm_f32(x, w))
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError(f"linear: unsupported dtypes {x.dtype} x {w.dtype}")
     M, K = x.shape
     if _odd(x, w):
-        return ops.gemm_bf16_any(x, w, out_dtype)
+        return after(ops.gemm_bf16_any(x, w, out_dtype))
     if M <= STREAM_MAX_ROWS:
         if _streams(M, K, whole=True):
-            return ops.gemv_stream(x, w, out_dtype)
-        return ops.gemv_bf16(x, w, out_dtype)
+            return ops.gemv_stream(x, w, out_dtype, act=act)
+        return after(ops.gemv_bf16(x, w, out_dtype))
     if M <= 32 and ((M + 127) // 128) * ((w.shape[0] + 255) // 256) < sm_count(x.device) // 2:
         # too few output tiles to keep the SMs busy, and nothing downstream that could add up
         # partial sums: the streaming kernel's many small blocks still win here (measured)
-        return ops.gemv_bf16(x, w, out_dtype)
+        return after(ops.gemv_bf16(x, w, out_dtype))
     if _library_gemm and out_dtype == torch.bfloat16 and x.is_cuda:
-        return torch.matmul(x, w.t())
-    return ops.gemm_tc(x, w, out_dtype)
+        return after(torch.matmul(x, w.t()))
+    return ops.gemm_tc(x, w, out_dtype, act=act)
 
 
 def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, act=None) -> torch.Tensor:

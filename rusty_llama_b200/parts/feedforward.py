@@ -76,7 +76,8 @@ class GatedMLP(FeedForward):
 
 @FEED_FORWARDS.register("mlp")
 class MLP(FeedForward):
-    """f = W_down act(W_up x), no gate.  act "relu2": the square of relu, applied in 32-bit to the up product's values.
+    """f = W_down act(W_up x), no gate.  act "relu2": the square of relu, applied in 32-bit, in bfloat16 runs to the up product's
+    32-bit sums in its kernel's epilogue.
 
     params: hidden_size, intermediate_size, activation ("relu2"), names (optional: keys up down).
     tensors: <prefix>up_proj.weight [ff, d], down_proj.weight [d, ff]."""
@@ -101,5 +102,5 @@ class MLP(FeedForward):
         self.w_down = tensors[p + self.names["down"]].contiguous()
 
     def forward(self, xn: torch.Tensor, step) -> torch.Tensor:
-        h = ops.unary_act(linear(xn, self.w_up), ops.ACT_RELU2)
-        return linear_to_stream(h, self.w_down)
+        # (the streaming and the tcgen05 product apply the activation to their 32-bit sums; behind the others it is a pass of its own)
+        return linear_to_stream(linear(xn, self.w_up, act=self.activation), self.w_down)

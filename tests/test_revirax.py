@@ -715,3 +715,23 @@ def test_min_gru_in_stretches(dtype, width):
     want = np.concatenate([ref[0][37:], ref[1], ref[2]])
     assert np.abs(out.to(torch.float64).cpu().numpy() - want).max() <= _tol(dtype, 2e-5, 1.5e-2) * max(1.0, np.abs(want).max())
     assert float(state[1].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("M, N, K", [(3, 200, 128), (8, 4096, 1024), (200, 520, 256), (2048, 1024, 512), (20, 96, 68), (5, 64, 100)])
+def test_products_with_the_squared_relu_in_their_epilogue(M, N, K):
+    """`linear(..., act="relu2")` on every route it takes (the streaming kernel, the tcgen05 kernel, and the kernels behind which
+    the activation is a pass of its own): the activation must see the 32-bit sums, and rows and columns beside the result stay."""
+    from rusty_llama_b200.kernels.linear import linear
+
+    rng = np.random.default_rng(M + N)
+    x = _rounded(rng.standard_normal((M, K)), torch.bfloat16)
+    w = _rounded(rng.standard_normal((N, K)) / np.sqrt(K), torch.bfloat16)
+    out = linear(_dev(x, torch.bfloat16), _dev(w, torch.bfloat16), act="relu2").to(torch.float64).cpu().numpy()
+    ref = np.maximum(x @ w.T, 0.0) ** 2
+    assert out.shape == ref.shape
+    assert np.abs(out - ref).max() <= 1.2e-2 * max(1.0, np.abs(ref).max())
+    x32 = _dev(x, torch.float32)
+    out32 = linear(x32, _dev(w, torch.float32), act="relu2").to(torch.float64).cpu().numpy()
+    assert np.abs(out32 - ref).max() <= 2e-5 * max(1.0, np.abs(ref).max())
+    from rusty_llama_b200.kernels import ops
+    ops.tc_status_check()
