@@ -151,13 +151,30 @@ decay_chunk_state_kernel(const T* __restrict__ k, const T* __restrict__ v, int i
   if (n <= 0) return;
   float* k_s = sm;             // [DC][dim], weighted by lam^(n-1-i)
   float* v_s = sm + DC * dim;  // [DC][DC_COLS]
+  __shared__ float pw[DC];
   const float lam = decay[h];
-  for (int idx = threadIdx.x; idx < n * dim; idx += 256) {
-    const int i = idx / dim, r = idx - i * dim;
-    float kv = to_f32(k[(size_t)(t0 + i) * in_stride + (size_t)h * dim + r]);
-    if (act) kv = silu_f(kv);
-    k_s[idx] = kv * powf(lam, (float)(n - 1 - i));
+  if (threadIdx.x < DC) pw[threadIdx.x] = powf(lam, (float)threadIdx.x);
+  __syncthreads();
+  if (sizeof(T) == 2 && ((dim | in_stride) & 7) == 0 && (((uintptr_t)k) & 15) == 0) {  // sixteen bytes a load
+#pragma unroll 2
+    for (int idx = threadIdx.x; idx < n * (dim / 8); idx += 256) {
+      const int i = idx / (dim / 8), r = 8 * (idx - i * (dim / 8));
+      float f[8];
+      bf16x8_to_f32(__ldcg(reinterpret_cast<const uint4*>(k + (size_t)(t0 + i) * in_stride + (size_t)h * dim + r)), f);
+      const float w = pw[n - 1 - i];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) k_s[i * dim + r + e] = (act ? silu_f(f[e]) : f[e]) * w;
+    }
+  } else {
+#pragma unroll 4
+    for (int idx = threadIdx.x; idx < n * dim; idx += 256) {
+      const int i = idx / dim, r = idx - i * dim;
+      float kv = to_f32(k[(size_t)(t0 + i) * in_stride + (size_t)h * dim + r]);
+      if (act) kv = silu_f(kv);
+      k_s[idx] = kv * pw[n - 1 - i];
+    }
   }
+#pragma unroll 4
   for (int idx = threadIdx.x; idx < n * DC_COLS; idx += 256) {
     const int i = idx / DC_COLS, cc = idx - i * DC_COLS;
     float vv = 0.f;
@@ -212,11 +229,21 @@ __global__ void decay_chunk_scan_kernel(const float* __restrict__ decay, float* 
   float* u = scratch + (size_t)blockIdx.x * max_chunks * elems + e;
   float S = *st;
   const float lam_full = powf(lam, (float)DC);
-  for (int c = 0; c * DC < len; ++c) {
-    const int n = min(DC, len - c * DC);
-    const float add = u[(size_t)c * elems];
-    u[(size_t)c * elems] = S;
-    S = (n == DC ? lam_full : powf(lam, (float)n)) * S + add;
+  const int n_chunks = (len + DC - 1) / DC;
+  for (int c0 = 0; c0 < n_chunks; c0 += 8) {  // eight chunks' additions are asked for at once, then taken in order
+    float add[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (c0 + j < n_chunks) add[j] = __ldcg(u + (size_t)(c0 + j) * elems);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int c = c0 + j;
+      if (c < n_chunks) {
+        const int n = min(DC, len - c * DC);
+        u[(size_t)c * elems] = S;
+        S = (n == DC ? lam_full : powf(lam, (float)n)) * S + add[j];
+      }
+    }
   }
   *st = S;
 }
@@ -338,6 +365,251 @@ decay_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ k, const T
   }
 }
 
+// (3) on the tensor cores, for bfloat16 runs with key and value sizes up to 128: a block of four warps per (sequence, head, chunk),
+// a warp per 16 tokens.  q, k, v go to shared memory as bfloat16 after their activation (they are activations of projections);
+// the chunk's scores Q K^T come from mma.sync with 32-bit sums, are decayed and masked in 32-bit, and meet the values as TWO
+// bfloat16 numbers each (the score rounded, and what the rounding left), so the weighted sum sees 16 digits of them; the state
+// before the chunk, which is 32-bit, meets the queries the same way, as two bfloat16 halves that take the place of the chunk's
+// keys and values in shared memory one after the other.
+__device__ __forceinline__ void rc_ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void rc_ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void rc_mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// a 32-bit number as two bfloat16: hi = the number rounded, lo = what the rounding left
+__device__ __forceinline__ void rc_split(float v, bf16& hi, bf16& lo) {
+  hi = __float2bfloat16_rn(v);
+  lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+}
+__device__ __forceinline__ uint32_t rc_pack(bf16 a, bf16 b) {
+  __nv_bfloat162 v(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(128)
+decay_chunk_out_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v, int in_stride,
+                           const float* __restrict__ decay, const int* __restrict__ seq_start, const float* __restrict__ scratch,
+                           int max_chunks, float* __restrict__ out, int out_stride, int H, int dim, int vdim, int act) {
+  constexpr int STRIDE = HD + 8;
+  constexpr int KSTEPS = HD / 16;
+  extern __shared__ __align__(16) unsigned char rc_smem[];
+  bf16* q_s = reinterpret_cast<bf16*>(rc_smem);  // [DC][STRIDE]
+  bf16* k_s = q_s + DC * STRIDE;                 // [DC][STRIDE]
+  bf16* v_s = k_s + DC * STRIDE;                 // [DC][STRIDE]; k_s and v_s together later hold a half of the state, [2 DC >= HD][STRIDE]
+  __shared__ float pw[DC + 1];
+  const int s = blockIdx.x / H, h = blockIdx.x % H, c = blockIdx.y;
+  const int t0 = seq_start[s] + c * DC;
+  const int n = min(DC, seq_start[s + 1] - t0);
+  if (n <= 0) return;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t4 = lane & 3;
+  const float lam = decay[h];
+  for (int i = tid; i <= DC; i += 128) pw[i] = powf(lam, (float)i);
+  const bf16 zero = __float2bfloat16_rn(0.f);
+  const bool vec8 = ((dim | vdim | in_stride) & 7) == 0 && ((((uintptr_t)q) | ((uintptr_t)k) | ((uintptr_t)v)) & 15) == 0;
+  if (vec8) {  // sixteen bytes a load: eight numbers of q and k, or of v, per thread and round
+#pragma unroll 2
+    for (int idx = tid; idx < DC * (HD / 8); idx += 128) {
+      const int i = idx / (HD / 8), r = 8 * (idx - i * (HD / 8));
+      float qf[8], kf[8], vf[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) qf[e] = kf[e] = vf[e] = 0.f;
+      if (i < n) {
+        if (r < dim) {
+          const size_t at = (size_t)(t0 + i) * in_stride + (size_t)h * dim + r;
+          bf16x8_to_f32(__ldcg(reinterpret_cast<const uint4*>(q + at)), qf);
+          bf16x8_to_f32(__ldcg(reinterpret_cast<const uint4*>(k + at)), kf);
+        }
+        if (r < vdim) bf16x8_to_f32(__ldcg(reinterpret_cast<const uint4*>(v + (size_t)(t0 + i) * in_stride + (size_t)h * vdim + r)), vf);
+        if (act) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            qf[e] = silu_f(qf[e]);
+            kf[e] = silu_f(kf[e]);
+            vf[e] = silu_f(vf[e]);
+          }
+        }
+      }
+      uint4 qo, ko, vo;
+      qo.x = rc_pack(__float2bfloat16_rn(qf[0]), __float2bfloat16_rn(qf[1])); qo.y = rc_pack(__float2bfloat16_rn(qf[2]), __float2bfloat16_rn(qf[3]));
+      qo.z = rc_pack(__float2bfloat16_rn(qf[4]), __float2bfloat16_rn(qf[5])); qo.w = rc_pack(__float2bfloat16_rn(qf[6]), __float2bfloat16_rn(qf[7]));
+      ko.x = rc_pack(__float2bfloat16_rn(kf[0]), __float2bfloat16_rn(kf[1])); ko.y = rc_pack(__float2bfloat16_rn(kf[2]), __float2bfloat16_rn(kf[3]));
+      ko.z = rc_pack(__float2bfloat16_rn(kf[4]), __float2bfloat16_rn(kf[5])); ko.w = rc_pack(__float2bfloat16_rn(kf[6]), __float2bfloat16_rn(kf[7]));
+      vo.x = rc_pack(__float2bfloat16_rn(vf[0]), __float2bfloat16_rn(vf[1])); vo.y = rc_pack(__float2bfloat16_rn(vf[2]), __float2bfloat16_rn(vf[3]));
+      vo.z = rc_pack(__float2bfloat16_rn(vf[4]), __float2bfloat16_rn(vf[5])); vo.w = rc_pack(__float2bfloat16_rn(vf[6]), __float2bfloat16_rn(vf[7]));
+      *reinterpret_cast<uint4*>(q_s + i * STRIDE + r) = qo;
+      *reinterpret_cast<uint4*>(k_s + i * STRIDE + r) = ko;
+      *reinterpret_cast<uint4*>(v_s + i * STRIDE + r) = vo;
+    }
+  } else {
+#pragma unroll 4
+    for (int idx = tid; idx < DC * HD; idx += 128) {
+      const int i = idx / HD, r = idx - i * HD;
+      float qv = 0.f, kv = 0.f, vv = 0.f;
+      if (i < n) {
+        if (r < dim) {
+          const size_t at = (size_t)(t0 + i) * in_stride + (size_t)h * dim + r;
+          qv = __bfloat162float(q[at]);
+          kv = __bfloat162float(k[at]);
+          if (act) {
+            qv = silu_f(qv);
+            kv = silu_f(kv);
+          }
+        }
+        if (r < vdim) {
+          vv = __bfloat162float(v[(size_t)(t0 + i) * in_stride + (size_t)h * vdim + r]);
+          if (act) vv = silu_f(vv);
+        }
+      }
+      q_s[i * STRIDE + r] = __float2bfloat16_rn(qv);
+      k_s[i * STRIDE + r] = __float2bfloat16_rn(kv);
+      v_s[i * STRIDE + r] = __float2bfloat16_rn(vv);
+    }
+  }
+  for (int idx = tid; idx < 3 * DC * 8; idx += 128) q_s[(idx >> 3) * STRIDE + HD + (idx & 7)] = zero;  // the rows' padding
+  __syncthreads();
+
+  // ---- the chunk's scores for this warp's 16 tokens against its 64 tokens
+  float s_acc[DC / 8][4];
+#pragma unroll
+  for (int i = 0; i < DC / 8; ++i) s_acc[i][0] = s_acc[i][1] = s_acc[i][2] = s_acc[i][3] = 0.f;
+#pragma unroll
+  for (int kk = 0; kk < KSTEPS; ++kk) {
+    uint32_t a[4];
+    rc_ldmatrix_x4(a, q_s + (size_t)(warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * STRIDE + kk * 16 + 8 * (lane >> 4));
+#pragma unroll
+    for (int np = 0; np < DC / 16; ++np) {
+      uint32_t b[4];
+      rc_ldmatrix_x4(b, k_s + (size_t)(np * 16 + (lane & 7) + 8 * (lane >> 4)) * STRIDE + kk * 16 + 8 * ((lane >> 3) & 1));
+      rc_mma_bf16(s_acc[2 * np], a, b[0], b[1]);
+      rc_mma_bf16(s_acc[2 * np + 1], a, b[2], b[3]);
+    }
+  }
+  // ---- decay and mask in 32-bit; each score as two bfloat16 numbers, laid out as the A operand of the next product
+  uint32_t p_hi[DC / 16][4], p_lo[DC / 16][4];
+  const int row[2] = {warp * 16 + g, warp * 16 + g + 8};
+#pragma unroll
+  for (int kk = 0; kk < DC / 16; ++kk) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {    // the two groups of 8 keys of this step
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {           // this thread's two rows
+        const int nn = 2 * kk + half;
+        bf16 hi[2], lo[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int j = nn * 8 + 2 * t4 + e;
+          const float p = (j <= row[r]) ? s_acc[nn][2 * r + e] * pw[row[r] - j] : 0.f;
+          rc_split(p, hi[e], lo[e]);
+        }
+        p_hi[kk][2 * half + r] = rc_pack(hi[0], hi[1]);
+        p_lo[kk][2 * half + r] = rc_pack(lo[0], lo[1]);
+      }
+    }
+  }
+  float intra[HD / 8][4], inter[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) {
+    intra[i][0] = intra[i][1] = intra[i][2] = intra[i][3] = 0.f;
+    inter[i][0] = inter[i][1] = inter[i][2] = inter[i][3] = 0.f;
+  }
+#pragma unroll
+  for (int kk = 0; kk < DC / 16; ++kk) {
+#pragma unroll
+    for (int dp = 0; dp < HD / 16; ++dp) {
+      uint32_t b[4];
+      rc_ldmatrix_x4_trans(b, v_s + (size_t)(kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * STRIDE + dp * 16 + 8 * (lane >> 4));
+      rc_mma_bf16(intra[2 * dp], p_hi[kk], b[0], b[1]);
+      rc_mma_bf16(intra[2 * dp + 1], p_hi[kk], b[2], b[3]);
+      rc_mma_bf16(intra[2 * dp], p_lo[kk], b[0], b[1]);
+      rc_mma_bf16(intra[2 * dp + 1], p_lo[kk], b[2], b[3]);
+    }
+  }
+  // ---- the queries against the state before the chunk, one bfloat16 half of it at a time in the keys' and values' place
+  const float* sp = scratch + ((size_t)blockIdx.x * max_chunks + c) * dim * vdim;
+  bf16* st_s = k_s;  // [HD][STRIDE]: 2 DC rows >= HD
+  for (int pass = 0; pass < 2; ++pass) {
+    __syncthreads();  // the keys and values (or the first half) are no longer read
+    if ((vdim & 3) == 0) {  // four numbers a load, four loads in flight
+#pragma unroll 4
+      for (int idx = tid; idx < HD * (HD / 4); idx += 128) {
+        const int r = idx / (HD / 4), cc = 4 * (idx - r * (HD / 4));
+        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < dim && cc < vdim) t = __ldcg(reinterpret_cast<const float4*>(sp + (size_t)r * vdim + cc));
+        const float f[4] = {t.x, t.y, t.z, t.w};
+        bf16 o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          bf16 hi, lo;
+          rc_split(f[e], hi, lo);
+          o[e] = pass == 0 ? hi : lo;
+        }
+        uint2 raw;
+        raw.x = rc_pack(o[0], o[1]);
+        raw.y = rc_pack(o[2], o[3]);
+        *reinterpret_cast<uint2*>(st_s + r * STRIDE + cc) = raw;
+      }
+    } else {
+      for (int idx = tid; idx < HD * HD; idx += 128) {
+        const int r = idx / HD, cc = idx - r * HD;
+        bf16 hi = zero, lo = zero;
+        if (r < dim && cc < vdim) rc_split(sp[(size_t)r * vdim + cc], hi, lo);
+        st_s[r * STRIDE + cc] = pass == 0 ? hi : lo;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+      uint32_t a[4];
+      rc_ldmatrix_x4(a, q_s + (size_t)(warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * STRIDE + kk * 16 + 8 * (lane >> 4));
+#pragma unroll
+      for (int dp = 0; dp < HD / 16; ++dp) {
+        uint32_t b[4];
+        rc_ldmatrix_x4_trans(b, st_s + (size_t)(kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * STRIDE + dp * 16 + 8 * (lane >> 4));
+        rc_mma_bf16(inter[2 * dp], a, b[0], b[1]);
+        rc_mma_bf16(inter[2 * dp + 1], a, b[2], b[3]);
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int i = row[r];
+    if (i < n) {
+      const float w = pw[i + 1];
+      float* o = out + (size_t)(t0 + i) * out_stride + (size_t)h * vdim;
+#pragma unroll
+      for (int nn = 0; nn < HD / 8; ++nn) {
+        const int d = nn * 8 + 2 * t4;
+        if (d < vdim) o[d] = intra[nn][2 * r] + w * inter[nn][2 * r];
+        if (d + 1 < vdim) o[d + 1] = intra[nn][2 * r + 1] + w * inter[nn][2 * r + 1];
+      }
+    }
+  }
+}
+
+template <int HD>
+static cudaError_t launch_chunk_out_mma(dim3 grid, cudaStream_t stream, const void* q, const void* k, const void* v, int in_stride,
+                                        const float* decay, const int* seq_start, const float* scratch, int max_chunks, float* out,
+                                        int out_stride, int H, int dim, int vdim, int act) {
+  const size_t smem = (size_t)3 * DC * (HD + 8) * sizeof(bf16);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(decay_chunk_out_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  decay_chunk_out_mma_kernel<HD><<<grid, 128, smem, stream>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, in_stride, decay, seq_start, scratch,
+                                                              max_chunks, out, out_stride, H, dim, vdim, act);
+  return cudaGetLastError();
+}
+
 RL_API long long rl_decay_attn_chunked_scratch_floats(int n_seqs, int max_q_len, int H, int dim, int vdim) {
   return (long long)n_seqs * H * ((max_q_len + DC - 1) / DC) * dim * vdim;
 }
@@ -366,6 +638,25 @@ RL_API int rl_decay_attn_chunked(const void* q, const void* k, const void* v, in
     decay_chunk_out_kernel<T><<<grid, 256, smem3, stream>>>((const T*)q, (const T*)k, (const T*)v, in_stride, decay, seq_start, scratch,  \
                                                             max_chunks, out, out_stride, H, dim, vdim, act);                          \
   } while (0)
+  const int hd = dim > vdim ? dim : vdim;
+  if (dtype == RL_BF16 && hd <= 128) {
+    // the chunks' additions and the scan as above; the outputs on the tensor cores
+    if (cudaFuncSetAttribute(decay_chunk_state_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1) != cudaSuccess)
+      RL_REFUSE(4, "decay_attn_chunked: %zu bytes of shared memory refused", smem1);
+    decay_chunk_state_kernel<bf16><<<grid, 256, smem1, stream>>>((const bf16*)k, (const bf16*)v, in_stride, decay, seq_start, scratch, max_chunks,
+                                                                 H, dim, vdim, act);
+    decay_chunk_scan_kernel<<<grid2, 256, 0, stream>>>(decay, state, slot_ids, seq_start, scratch, max_chunks, H, elems);
+    dim3 grid3(n_seqs * H, max_chunks);
+    cudaError_t e;
+    if (hd <= 32) e = launch_chunk_out_mma<32>(grid3, stream, q, k, v, in_stride, decay, seq_start, scratch, max_chunks, out, out_stride, H, dim, vdim, act);
+    else if (hd <= 64) e = launch_chunk_out_mma<64>(grid3, stream, q, k, v, in_stride, decay, seq_start, scratch, max_chunks, out, out_stride, H, dim, vdim, act);
+    else e = launch_chunk_out_mma<128>(grid3, stream, q, k, v, in_stride, decay, seq_start, scratch, max_chunks, out, out_stride, H, dim, vdim, act);
+    if (e != cudaSuccess) {
+      snprintf(rl_error_buf, sizeof(rl_error_buf), "%s", cudaGetErrorString(e));
+      return (int)e;
+    }
+    return 0;
+  }
   if (dtype == RL_BF16) RL_DAC(bf16);
   else if (dtype == RL_F32) RL_DAC(float);
   else RL_REFUSE(5, "decay_attn_chunked: unknown dtype %d", dtype);

@@ -687,7 +687,9 @@ def test_chunked_decay_attention_on_a_ragged_step(dtype, H, dim, vdim):
             kw = dict(max_q_len=163, scratch=torch.full((ops.decay_attn_chunked_scratch_floats(4, 163, H, dim, vdim),), float("nan"), device="cuda"))
         out = ops.decay_attn(q, k, v, dec, state, _i32([3, 0, 4, 1]), starts, H, dim, vdim, silu=True, **kw).to(torch.float64).cpu().numpy()
         want = np.concatenate([ref[0][37:], ref[1], ref[2], ref[3]])
-        assert np.abs(out - want).max() <= 5e-5 * max(1.0, np.abs(want).max()), how
+        # (in bfloat16 and up to size 128 the chunked outputs come from the tensor cores: q, k, v rounded after their activation)
+        tol = 1.5e-2 if (how == "chunked" and dtype == torch.bfloat16 and max(dim, vdim) <= 128) else 5e-5
+        assert np.abs(out - want).max() <= tol * max(1.0, np.abs(want).max()), how
         states[how] = state.cpu().numpy()
     assert np.abs(states["chunked"] - states["plain"]).max() <= 5e-5 * max(1.0, np.abs(states["plain"]).max())
     assert np.abs(states["chunked"][2]).max() == 0.0
