@@ -109,7 +109,7 @@ def kernel_table(z: dict, T: int, batch: int, ctx: int, peaks: dict) -> Dict[str
             else:  # a decode step: the rows of a block are the heads (as `Attention` plans it)
                 from .device import sm_count
                 pages = (min(W, pos0 + 1) + 63) // 64 + 1
-                n_splits = max(1, min(2 * sm_count() // n_seqs, pages // 2, 64))
+                n_splits = max(1, min(2 * sm_count() // n_seqs, pages, 64))
                 sc = torch.empty(ops.flash_mix_decode_scratch_floats(n_seqs, H, hd, n_splits), device=dev)
                 us = mb._time(lambda i: ops.flash_mix_decode(qf, kp, vp, table, p0, H, G, hd, hd, scale, n_splits, sc, window=W, gate=gate), 1, **it)
             # its products: the scores against the keys of all kv heads, and the values

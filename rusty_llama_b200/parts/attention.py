@@ -182,13 +182,13 @@ class Attention(Mixer):
                 and (out is None or (out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0)) and (self.qd + self.kvd + self.vvd) % 2 == 0):
             if step.decode_only and ops.flash_mix_decode_takes(self.H, self.K, self.hd, self.vd):
                 # single tokens: all heads of a sequence are the rows of one block, which reads a key tile once for all of them;
-                # the key range is cut into parts of at least two pages so that the blocks fill the GPU once
+                # the key range is cut into parts of a page or more so that the blocks fill the GPU (a block is one or two warps: short chains matter more than few parts)
                 if self.fold_matrix is None:
                     self.fold_matrix = self.mix if self.has_mix else torch.eye(self.H, dtype=torch.float32, device=xn.device)
                 qf = ops.fold_queries(proj, self.fold_matrix, self.H, self.K, self.hd)
                 keys = min(self.window, step.plan_kv_len) if self.window else step.plan_kv_len
                 pages = (keys + ops.PAGE_SIZE - 1) // ops.PAGE_SIZE + 1
-                n_splits = max(1, min(2 * sm_count(xn.device) // step.n_seqs, pages // 2, 64))
+                n_splits = max(1, min(2 * sm_count(xn.device) // step.n_seqs, pages, 64))
                 scratch = self.rt.workspace.get("flash_mix_decode", ops.flash_mix_decode_scratch_floats(step.n_seqs, self.H, self.vd, n_splits), torch.float32)
                 a = ops.flash_mix_decode(
                     qf, cache.k_pages, cache.v_pages, cache.block_table, step.seq_pos0, self.H, self.K, self.hd, self.vd, self.scale,
