@@ -596,6 +596,127 @@ decay_chunk_out_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ 
   }
 }
 
+// (1) on the tensor cores, for bfloat16 runs with key and value sizes of 33 to 128: U = (K w)^T V over the chunk's tokens, with the
+// decay-weighted keys (32-bit) as two bfloat16 halves and the values as bfloat16 after their activation.  A block of four warps
+// per (sequence, head, chunk); warp w owns rows HD/4 w .. of U.  The keys lie in shared memory as [token][dim], which is the
+// transpose of the product's first operand: `ldmatrix.trans` turns each 8 x 8 piece as it loads it.
+template <int HD>
+__global__ void __launch_bounds__(128)
+decay_chunk_state_mma_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v, int in_stride, const float* __restrict__ decay,
+                             const int* __restrict__ seq_start, float* __restrict__ scratch, int max_chunks, int H, int dim, int vdim, int act) {
+  constexpr int STRIDE = HD + 8;
+  constexpr int MT = HD / 64;  // 16-row tiles per warp
+  extern __shared__ __align__(16) unsigned char rc_smem[];
+  bf16* kh_s = reinterpret_cast<bf16*>(rc_smem);  // [DC][STRIDE] the weighted keys, rounded
+  bf16* kl_s = kh_s + DC * STRIDE;                // [DC][STRIDE] what the rounding left
+  bf16* v_s = kl_s + DC * STRIDE;                 // [DC][STRIDE]
+  __shared__ float pw[DC];
+  const int s = blockIdx.x / H, h = blockIdx.x % H, c = blockIdx.y;
+  const int t0 = seq_start[s] + c * DC;
+  const int n = min(DC, seq_start[s + 1] - t0);
+  if (n <= 0) return;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t4 = lane & 3;
+  const float lam = decay[h];
+  if (tid < DC) pw[tid] = powf(lam, (float)tid);
+  __syncthreads();
+  const bool vec8 = ((dim | vdim | in_stride) & 7) == 0 && ((((uintptr_t)k) | ((uintptr_t)v)) & 15) == 0;
+  for (int idx = tid; idx < DC * (HD / 8); idx += 128) {
+    const int i = idx / (HD / 8), r = 8 * (idx - i * (HD / 8));
+    float kf[8], vf[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) kf[e] = vf[e] = 0.f;
+    if (i < n) {
+      const size_t row = (size_t)(t0 + i) * in_stride;
+      if (vec8) {
+        if (r < dim) bf16x8_to_f32(__ldcg(reinterpret_cast<const uint4*>(k + row + (size_t)h * dim + r)), kf);
+        if (r < vdim) bf16x8_to_f32(__ldcg(reinterpret_cast<const uint4*>(v + row + (size_t)h * vdim + r)), vf);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          if (r + e < dim) kf[e] = __bfloat162float(k[row + (size_t)h * dim + r + e]);
+          if (r + e < vdim) vf[e] = __bfloat162float(v[row + (size_t)h * vdim + r + e]);
+        }
+      }
+      const float w = pw[n - 1 - i];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        kf[e] = (act ? silu_f(kf[e]) : kf[e]) * w;
+        if (act) vf[e] = silu_f(vf[e]);
+      }
+    }
+    bf16 hi[8], lo[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) rc_split(kf[e], hi[e], lo[e]);
+    uint4 ho, lo4, vo;
+    ho.x = rc_pack(hi[0], hi[1]); ho.y = rc_pack(hi[2], hi[3]); ho.z = rc_pack(hi[4], hi[5]); ho.w = rc_pack(hi[6], hi[7]);
+    lo4.x = rc_pack(lo[0], lo[1]); lo4.y = rc_pack(lo[2], lo[3]); lo4.z = rc_pack(lo[4], lo[5]); lo4.w = rc_pack(lo[6], lo[7]);
+    vo.x = rc_pack(__float2bfloat16_rn(vf[0]), __float2bfloat16_rn(vf[1])); vo.y = rc_pack(__float2bfloat16_rn(vf[2]), __float2bfloat16_rn(vf[3]));
+    vo.z = rc_pack(__float2bfloat16_rn(vf[4]), __float2bfloat16_rn(vf[5])); vo.w = rc_pack(__float2bfloat16_rn(vf[6]), __float2bfloat16_rn(vf[7]));
+    *reinterpret_cast<uint4*>(kh_s + i * STRIDE + r) = ho;
+    *reinterpret_cast<uint4*>(kl_s + i * STRIDE + r) = lo4;
+    *reinterpret_cast<uint4*>(v_s + i * STRIDE + r) = vo;
+  }
+  __syncthreads();
+  float acc[MT][HD / 8][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) acc[mt][i][0] = acc[mt][i][1] = acc[mt][i][2] = acc[mt][i][3] = 0.f;
+#pragma unroll
+  for (int kk = 0; kk < DC / 16; ++kk) {
+    uint32_t a_hi[MT][4], a_lo[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      const int r0 = warp * (HD / 4) + mt * 16;
+      const size_t at = (size_t)(kk * 16 + 8 * (lane >> 4) + (lane & 7)) * STRIDE + r0 + 8 * ((lane >> 3) & 1);
+      rc_ldmatrix_x4_trans(a_hi[mt], kh_s + at);
+      rc_ldmatrix_x4_trans(a_lo[mt], kl_s + at);
+    }
+#pragma unroll
+    for (int dp = 0; dp < HD / 16; ++dp) {
+      uint32_t b[4];
+      rc_ldmatrix_x4_trans(b, v_s + (size_t)(kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * STRIDE + dp * 16 + 8 * (lane >> 4));
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        rc_mma_bf16(acc[mt][2 * dp], a_hi[mt], b[0], b[1]);
+        rc_mma_bf16(acc[mt][2 * dp + 1], a_hi[mt], b[2], b[3]);
+        rc_mma_bf16(acc[mt][2 * dp], a_lo[mt], b[0], b[1]);
+        rc_mma_bf16(acc[mt][2 * dp + 1], a_lo[mt], b[2], b[3]);
+      }
+    }
+  }
+  float* u = scratch + ((size_t)blockIdx.x * max_chunks + c) * dim * vdim;
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = warp * (HD / 4) + mt * 16 + g + 8 * half;
+      if (r < dim) {
+#pragma unroll
+        for (int nn = 0; nn < HD / 8; ++nn) {
+          const int col = nn * 8 + 2 * t4;
+          if (col < vdim) u[(size_t)r * vdim + col] = acc[mt][nn][2 * half];
+          if (col + 1 < vdim) u[(size_t)r * vdim + col + 1] = acc[mt][nn][2 * half + 1];
+        }
+      }
+    }
+  }
+}
+
+template <int HD>
+static cudaError_t launch_chunk_state_mma(dim3 grid, cudaStream_t stream, const void* k, const void* v, int in_stride, const float* decay,
+                                          const int* seq_start, float* scratch, int max_chunks, int H, int dim, int vdim, int act) {
+  const size_t smem = (size_t)3 * DC * (HD + 8) * sizeof(bf16);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(decay_chunk_state_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  decay_chunk_state_mma_kernel<HD><<<grid, 128, smem, stream>>>((const bf16*)k, (const bf16*)v, in_stride, decay, seq_start, scratch, max_chunks, H,
+                                                                dim, vdim, act);
+  return cudaGetLastError();
+}
+
 template <int HD>
 static cudaError_t launch_chunk_out_mma(dim3 grid, cudaStream_t stream, const void* q, const void* k, const void* v, int in_stride,
                                         const float* decay, const int* seq_start, const float* scratch, int max_chunks, float* out,
@@ -641,13 +762,23 @@ RL_API int rl_decay_attn_chunked(const void* q, const void* k, const void* v, in
   const int hd = dim > vdim ? dim : vdim;
   if (dtype == RL_BF16 && hd <= 128) {
     // the chunks' additions and the scan as above; the outputs on the tensor cores
-    if (cudaFuncSetAttribute(decay_chunk_state_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1) != cudaSuccess)
-      RL_REFUSE(4, "decay_attn_chunked: %zu bytes of shared memory refused", smem1);
-    decay_chunk_state_kernel<bf16><<<grid, 256, smem1, stream>>>((const bf16*)k, (const bf16*)v, in_stride, decay, seq_start, scratch, max_chunks,
-                                                                 H, dim, vdim, act);
-    decay_chunk_scan_kernel<<<grid2, 256, 0, stream>>>(decay, state, slot_ids, seq_start, scratch, max_chunks, H, elems);
     dim3 grid3(n_seqs * H, max_chunks);
-    cudaError_t e;
+    cudaError_t e = cudaSuccess;
+    if (hd > 64) {
+      e = launch_chunk_state_mma<128>(grid3, stream, k, v, in_stride, decay, seq_start, scratch, max_chunks, H, dim, vdim, act);
+    } else if (hd > 32) {
+      e = launch_chunk_state_mma<64>(grid3, stream, k, v, in_stride, decay, seq_start, scratch, max_chunks, H, dim, vdim, act);
+    } else {
+      if (cudaFuncSetAttribute(decay_chunk_state_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1) != cudaSuccess)
+        RL_REFUSE(4, "decay_attn_chunked: %zu bytes of shared memory refused", smem1);
+      decay_chunk_state_kernel<bf16><<<grid, 256, smem1, stream>>>((const bf16*)k, (const bf16*)v, in_stride, decay, seq_start, scratch, max_chunks,
+                                                                   H, dim, vdim, act);
+    }
+    if (e != cudaSuccess) {
+      snprintf(rl_error_buf, sizeof(rl_error_buf), "%s", cudaGetErrorString(e));
+      return (int)e;
+    }
+    decay_chunk_scan_kernel<<<grid2, 256, 0, stream>>>(decay, state, slot_ids, seq_start, scratch, max_chunks, H, elems);
     if (hd <= 32) e = launch_chunk_out_mma<32>(grid3, stream, q, k, v, in_stride, decay, seq_start, scratch, max_chunks, out, out_stride, H, dim, vdim, act);
     else if (hd <= 64) e = launch_chunk_out_mma<64>(grid3, stream, q, k, v, in_stride, decay, seq_start, scratch, max_chunks, out, out_stride, H, dim, vdim, act);
     else e = launch_chunk_out_mma<128>(grid3, stream, q, k, v, in_stride, decay, seq_start, scratch, max_chunks, out, out_stride, H, dim, vdim, act);

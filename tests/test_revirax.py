@@ -655,7 +655,7 @@ def test_tensor_core_attention_with_options(H, G, kd, vd, window, talk, use_sink
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H, dim, vdim", [(2, 24, 40), (1, 72, 8), (2, 128, 64), (1, 256, 200)])
+@pytest.mark.parametrize("H, dim, vdim", [(2, 24, 40), (1, 72, 8), (2, 128, 64), (1, 256, 200), (2, 16, 32), (2, 64, 128), (1, 100, 50)])
 def test_chunked_decay_attention_on_a_ragged_step(dtype, H, dim, vdim):
     """The chunk-by-chunk kernels on a step of four sequences of 163 (going on from a state that 37 tokens have left), 64, 65
     and 1 tokens, against the plain recurrence; the states they leave must be those the token-by-token kernel leaves."""
@@ -691,7 +691,9 @@ def test_chunked_decay_attention_on_a_ragged_step(dtype, H, dim, vdim):
         tol = 1.5e-2 if (how == "chunked" and dtype == torch.bfloat16 and max(dim, vdim) <= 128) else 5e-5
         assert np.abs(out - want).max() <= tol * max(1.0, np.abs(want).max()), how
         states[how] = state.cpu().numpy()
-    assert np.abs(states["chunked"] - states["plain"]).max() <= 5e-5 * max(1.0, np.abs(states["plain"]).max())
+    # (up to size 128 the chunked kernels of a bfloat16 run take the values as bfloat16 after their activation)
+    tol = 1e-2 if (dtype == torch.bfloat16 and max(dim, vdim) <= 128) else 5e-5
+    assert np.abs(states["chunked"] - states["plain"]).max() <= tol * max(1.0, np.abs(states["plain"]).max())
     assert np.abs(states["chunked"][2]).max() == 0.0
 
 
