@@ -67,9 +67,11 @@ class Attention(Mixer):
              serves them all (src/backend/cuda.rs:423-442).
 
     A plain attention, with or without a sink, runs on the kernels built for it (tensor-core prompt attention, TMA-fed
-    decode attention, the rotation fused with the cache write or with the decode kernel).  With any other option, in a 32-bit run
-    with a sink, or with a head size that is no multiple of 8 it runs on `qkv_prep` and `attn_ext` (csrc/attention_ext.cu),
-    which take every option, every size and both element types."""
+    decode attention, the rotation fused with the cache write or with the decode kernel).  With any other option (and with a
+    sink in a 32-bit run, or at a head size that is no multiple of 8) it runs on `qkv_prep` and then, in bfloat16 at sizes in
+    multiples of 8, on the tensor-core kernels of csrc/attention_mix_mma.cu (`flash_mix` for prompts, `flash_mix_decode` for
+    single tokens, mixed scores through `fold_queries`), else on `attn_ext` (csrc/attention_ext.cu), which takes every option,
+    every size and both element types."""
 
     takes_out = True
 
